@@ -20,8 +20,13 @@ values live in one device slab per group, indexed by those ids.
   worker/src/inference/torch_engine.py:439-446).  Row ``max_seats`` of each table
   is the padding seat: all its entries name the spare page.
 * State slots: one tensor ``[max_seats + 1, *shape]`` per slot that declares a
-  :class:`~distie_b200.parts.base.StateNeed`, zeroed when a seat is opened.  The
-  Qwen2 decoder declares none; the structure is there all the same.
+  :class:`~distie_b200.parts.base.StateNeed` (a dict of tensors for a slot that declares
+  several by name), zeroed when a seat is opened and when a request is sent back to be
+  recomputed.  Layers with a recurrence keep their matrix state and the last inputs of
+  their short convolutions here.
+* A group whose need names a ``chunk`` gives pages back like a windowed one: no later
+  position reads a key from before the chunk the request is in.  A group whose values
+  have another size than its keys keeps two slabs instead of one.
 
 With ``device=None`` the manager keeps only the bookkeeping (no slabs), which is
 what the scheduler tests and sizing estimates use.
@@ -52,7 +57,7 @@ def pages_needed(tokens: int, page_size: int) -> int:
 def pages_that_fit(cache_needs, page_size: int, element_size: int, budget_bytes: int) -> int:
     """How many pages per group ``budget_bytes`` of device memory hold (the spare page of every slab included
     in the budget, not in the count): every cache slot keeps keys and values of its own for each page id."""
-    per_page = sum(2 * need.num_kv_heads * need.head_dim * element_size * page_size for need in cache_needs.values())
+    per_page = sum(need.num_kv_heads * (need.head_dim + need.v_dim) * element_size * page_size for need in cache_needs.values())
     if per_page <= 0:
         raise ValueError("the model declares no cache to size")
     return int(budget_bytes // per_page) - 1
@@ -88,14 +93,16 @@ class KvGroup:
         self._uploaded = None  # CUDA event after the last upload: the pinned table waits for it before it changes
 
     def bytes_per_token(self, element_size: int) -> int:
-        return 2 * len(self.slots) * self.need.num_kv_heads * self.need.head_dim * element_size
+        return len(self.slots) * self.need.num_kv_heads * (self.need.head_dim + self.need.v_dim) * element_size
 
     # -- bookkeeping --------------------------------------------------------
     def first_needed_page(self, cached: int) -> int:
         """Logical index of the first page a position >= cached can still see."""
-        if self.need.window is None:
-            return 0
-        first_key = max(0, cached - int(self.need.window) + 1)
+        first_key = 0
+        if self.need.window is not None:
+            first_key = max(first_key, cached - int(self.need.window) + 1)
+        if self.need.chunk is not None:
+            first_key = max(first_key, cached // int(self.need.chunk) * int(self.need.chunk))
         return first_key // self.page_size
 
     def missing(self, seat: int | None, tokens: int) -> int:
@@ -130,7 +137,7 @@ class KvGroup:
 
     def trim(self, seat: int, cached: int) -> int:
         held = self.seats.get(seat)
-        if held is None or self.need.window is None:
+        if held is None or (self.need.window is None and self.need.chunk is None):
             return 0
         keep_from = min(self.first_needed_page(cached), held.first + len(held.ids))
         drop = keep_from - held.first
@@ -160,8 +167,13 @@ class KvGroup:
 
     # -- device side --------------------------------------------------------
     def allocate_device(self, dtype: torch.dtype, device: torch.device) -> None:
-        shape = (len(self.slots), 2, self.num_pages + 1, self.need.num_kv_heads, self.page_size, self.need.head_dim)
-        self.slab = torch.zeros(shape, dtype=dtype, device=device)
+        rows = (self.num_pages + 1, self.need.num_kv_heads, self.page_size)
+        if self.need.v_dim == self.need.head_dim:
+            self.slab = torch.zeros((len(self.slots), 2, *rows, self.need.head_dim), dtype=dtype, device=device)
+            self._keys, self._values = self.slab[:, 0], self.slab[:, 1]
+        else:  # values of another size than keys: a slab each
+            self._keys = torch.zeros((len(self.slots), *rows, self.need.head_dim), dtype=dtype, device=device)
+            self._values = torch.zeros((len(self.slots), *rows, self.need.v_dim), dtype=dtype, device=device)
         self._host_tensor = torch.from_numpy(self.host_table)
         if device.type == "cuda":
             self._host_tensor = self._host_tensor.pin_memory()
@@ -188,7 +200,7 @@ class KvGroup:
         view = self._views.get(slot)
         if view is None:
             index = self.slots.index(slot)
-            view = KvSlot(self.slab[index, 0], self.slab[index, 1], self.device_table, self.page_size, self.num_pages + 1)
+            view = KvSlot(self._keys[index], self._values[index], self.device_table, self.page_size, self.num_pages + 1)
             self._views[slot] = view
         return view
 
@@ -227,14 +239,17 @@ class CacheManager:
         ]
         self._group_of = {slot: group for group in self.groups for slot in group.slots}
         self.state_needs = dict(state_needs or {})
-        self.states: dict[int, torch.Tensor] = {}
+        self.states: dict[int, torch.Tensor | dict[str, torch.Tensor]] = {}
         self._free_seats = list(range(max_seats - 1, -1, -1))
         self._open: set[int] = set()
         if self.device is not None:
             for group in self.groups:
                 group.allocate_device(dtype, self.device)
+            def make(need: StateNeed) -> torch.Tensor:
+                return torch.zeros((max_seats + 1, *need.shape), dtype=need.dtype, device=self.device)
+
             for slot, need in self.state_needs.items():
-                self.states[slot] = torch.zeros((max_seats + 1, *need.shape), dtype=need.dtype, device=self.device)
+                self.states[slot] = make(need) if isinstance(need, StateNeed) else {n: make(item) for n, item in need.items()}
 
     # -- seats --------------------------------------------------------------
     @property
@@ -246,9 +261,23 @@ class CacheManager:
             raise CacheExhausted(f"all {self.max_seats} seats are taken")
         seat = self._free_seats.pop()
         self._open.add(seat)
-        for state in self.states.values():
-            state[seat].zero_()
+        self._clear_state(seat)
         return seat
+
+    def state_tensors(self) -> list[torch.Tensor]:
+        """Every per-request state tensor, ``[max_seats + 1, ...]`` each, in a fixed order."""
+        out = []
+        for slot in sorted(self.states):
+            held = self.states[slot]
+            out += [held] if isinstance(held, torch.Tensor) else [held[name] for name in sorted(held)]
+        return out
+
+    def _clear_state(self, seat: int) -> None:
+        for state in self.state_tensors():
+            state[seat].zero_()
+
+    def state_bytes_per_seat(self) -> int:
+        return sum(t[0].numel() * t.element_size() for t in self.state_tensors())
 
     def close_seat(self, seat: int) -> None:
         if seat not in self._open:
@@ -264,8 +293,7 @@ class CacheManager:
             raise ValueError(f"seat {seat} is not open")
         for group in self.groups:
             group.release(seat)
-        for state in self.states.values():
-            state[seat].zero_()
+        self._clear_state(seat)
 
     # -- pages --------------------------------------------------------------
     def fits_ever(self, tokens: int) -> bool:

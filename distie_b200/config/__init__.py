@@ -3,6 +3,7 @@
 from .engine_config import EngineConfig, resolve_dtype_name
 from .model_spec import LayerCall, LayerSpec, ModelSpec, PartSpec
 from .qwen2_config import ConfigError, Qwen2Config
+from .zelasun_config import ZelasunConfig
 from .registry import (
     Architecture,
     architecture_of,
@@ -22,6 +23,7 @@ __all__ = [
     "ModelSpec",
     "PartSpec",
     "Qwen2Config",
+    "ZelasunConfig",
     "architecture_of",
     "get_architecture",
     "known_architectures",

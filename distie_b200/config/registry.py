@@ -1,7 +1,8 @@
 """One registry from an architecture's name to its configuration class and recipe.
 
 The reference hard-codes its one model (worker/src/inference/torch_engine.py:142);
-here the name in ``config.json["architectures"][0]`` selects an entry, everywhere:
+here the name in ``config.json["architectures"][0]`` (or, in configurations that name one
+design only, the string ``config.json["architecture"]``) selects an entry, everywhere:
 the loader, the random-weights writer, generation and trace replay.
 
 An entry is ``(config_cls, recipe)``: ``config_cls.from_dict(raw_json)`` gives the
@@ -56,8 +57,12 @@ def get_architecture(name: str) -> Architecture:
 
 def architecture_of(raw: Mapping[str, Any]) -> Architecture:
     names = raw.get("architectures") or ()
+    if isinstance(names, str):
+        names = (names,)
+    if not names and isinstance(raw.get("architecture"), str):
+        names = (raw["architecture"],)
     if not names:
-        raise KeyError("config.json has no 'architectures' entry to choose a model by")
+        raise KeyError("config.json has no 'architectures' (or 'architecture') entry to choose a model by")
     return get_architecture(names[0])
 
 

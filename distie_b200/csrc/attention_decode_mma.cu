@@ -103,7 +103,7 @@ attention_decode_mma_kernel(const ProjectionInput proj,
                             const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
                             const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                             int num_heads, int group_size, int head_chunks, int num_kv_heads, int page_size,
-                            int page_shift, int num_pages, int window, float scale_log2, int cluster_merge,
+                            int page_shift, int num_pages, int window, int key_chunk, float scale_log2, int cluster_merge,
                             int* __restrict__ error) {
   constexpr int CPR = D / 8;                 // 16-byte chunks per row of keys or values
   constexpr int ROW_BYTES = D * 2;
@@ -138,7 +138,7 @@ attention_decode_mma_kernel(const ProjectionInput proj,
   const int pos = positions[t];
   const int seat = seq_seat[token_seq[t]];
   const int* table = block_table + (size_t)seat * table_width;
-  const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int first = first_visible_key(pos, window, key_chunk);
   const int first_page = first / page_size;
   const int pages = pos / page_size - first_page + 1;
   const int pages_per_split = (pages + num_splits - 1) / num_splits;
@@ -625,7 +625,7 @@ static int launch_decode_mma(const ProjectionInput* proj, const void* q, int q_r
                              float* scratch, const int* positions, const int* token_seq, const int* seq_seat,
                              const int* block_table, int table_width, const void* k_cache, const void* v_cache,
                              int tokens, int num_heads, int num_kv_heads, int head_dim, int page_size, int num_pages,
-                             int window, float scale, int num_splits, int* error, cudaStream_t stream) {
+                             int window, int key_chunk, float scale, int num_splits, int* error, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
       num_splits < 1 || num_splits > 65535 || (num_splits > kMmaDecodeClusterSplits && scratch == nullptr) || (q_row_stride & 7) ||
@@ -689,7 +689,7 @@ static int launch_decode_mma(const ProjectionInput* proj, const void* q, int q_r
                          shared, stream, projection, (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, \
                          scratch_o, scratch_ml, positions, token_seq, seq_seat, block_table, table_width,          \
                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, num_heads, group, chunks,   \
-                         num_kv_heads, page_size, page_shift, num_pages, window, scale_log2, cluster_merge, error)
+                         num_kv_heads, page_size, page_shift, num_pages, window, key_chunk, scale_log2, cluster_merge, error)
 #define DISTIE_MMA_DECODE_BY_STAGES(DV, NV)   \
   if (stages == 2) { DISTIE_MMA_DECODE(DV, 2, NV) } \
   else { DISTIE_MMA_DECODE(DV, 3, NV) }
@@ -718,11 +718,11 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
                                            float* scratch, const int* positions, const int* token_seq,
                                            const int* seq_seat, const int* block_table, int table_width,
                                            const void* k_cache, const void* v_cache, int tokens, int num_heads,
-                                           int num_kv_heads, int head_dim, int page_size, int num_pages, int window,
+                                           int num_kv_heads, int head_dim, int page_size, int num_pages, int window, int key_chunk,
                                            float scale, int num_splits, int* error, cudaStream_t stream) {
   return launch_decode_mma(nullptr, q, q_row_stride, out, out_row_stride, scratch, positions, token_seq, seq_seat,
                            block_table, table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim,
-                           page_size, num_pages, window, scale, num_splits, error, stream);
+                           page_size, num_pages, window, key_chunk, scale, num_splits, error, stream);
 }
 
 // The same for a step of single tokens that starts from the q/k/v projection: `slices` [splits, tokens, row_stride]
@@ -735,7 +735,7 @@ extern "C" int distie_attention_decode_mma_qkv(const float* slices, int splits, 
                                                const int* positions, const int* token_seq, const int* seq_seat,
                                                const int* block_table, int table_width, void* k_cache, void* v_cache,
                                                int tokens, int num_heads, int num_kv_heads, int head_dim, int page_size,
-                                               int num_pages, int window, float scale, int num_splits, int* error,
+                                               int num_pages, int window, int key_chunk, float scale, int num_splits, int* error,
                                                cudaStream_t stream) {
   if (slices == nullptr || splits < 1 || row_stride < (num_heads + 2 * num_kv_heads) * head_dim) return DISTIE_ERR_ARG;
   if ((row_stride & 3) || (split_stride & 3) || ((uintptr_t)slices & 15) || ((uintptr_t)bias & 15)) return DISTIE_ERR_UNSUPPORTED;
@@ -750,5 +750,5 @@ extern "C" int distie_attention_decode_mma_qkv(const float* slices, int splits, 
   proj.write_new = write_new;
   return launch_decode_mma(&proj, nullptr, 8, out, out_row_stride, scratch, positions, token_seq, seq_seat, block_table,
                            table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim, page_size,
-                           num_pages, window, scale, num_splits, error, stream);
+                           num_pages, window, key_chunk, scale, num_splits, error, stream);
 }

@@ -49,6 +49,17 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// The oldest key the token at `pos` sees: all keys (window <= 0 and chunk <= 0), the last `window` of
+// them, or those of its own chunk of `chunk` positions, counted from position 0 of the request.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window, int chunk) {
+  int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (chunk > 0) {
+    const int start = pos / chunk * chunk;
+    if (start > first) first = start;
+  }
+  return first;
+}
+
 // Sum over a block of up to 1024 threads; `scratch` holds 32 floats of shared memory.
 // Every thread gets the result.  Safe to call repeatedly with the same scratch.
 __device__ __forceinline__ float block_sum(float v, float* scratch) {

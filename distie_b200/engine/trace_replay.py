@@ -33,7 +33,7 @@ from ..config.engine_config import EngineConfig
 from .batch import BatchEntry
 from .engine import Engine
 
-LIVE_REQUESTS = 8  # the protocol keeps up to four live; seats for twice that
+LIVE_REQUESTS = 4  # the protocol keeps up to four requests live: a seat (and a state slot) each
 
 
 class TraceSession:

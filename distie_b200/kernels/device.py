@@ -17,8 +17,10 @@ from __future__ import annotations
 
 import torch
 
+import ctypes
+
 from . import library
-from .interface import KernelSet, StepTensors
+from .interface import KernelSet, StepTensors, Terms
 from .library import KernelError, check, function
 
 _CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -27,6 +29,8 @@ _PREFILL_HEAD_DIMS = (64, 128)  # tensor-core attention for portions of prompts 
 _SKINNY_ROWS = 64               # weight-streaming products (tcgen05, weights as the 128-row operand) take up to 64 rows
 _CLUSTER_SPLITS = 8             # splits of a decode attention that one cluster of CTAs merges itself
 _TENSOR_CORE_ROWS = 128         # from here on the tcgen05 kernel's 128-row tiles are full; in between: the library
+_MAX_TERMS = 24                 # terms of a pending sum that the layer-norm kernel adds up itself
+_RULES = {"delta": 0, "ssd": 1}
 
 _ERROR_TEXT = {
     1: "a token id outside the vocabulary reached the embedding",
@@ -338,7 +342,7 @@ class DeviceKernels(KernelSet):
         return max(1, min(by_machine, by_length, 64))
 
     def qkv_attention(self, x, weight, bias, step, kv, writes_cache, rotary, num_heads, num_kv_heads, head_dim,
-                      window, scale, out) -> None:
+                      window, scale, out, chunk=None) -> None:
         """A step of single tokens on the tensor-core kernels: the attention kernel starts from the
         projection's float32 slices itself (bias, rotation, the token's key and value into the cache and into
         its own tile), so the kernel between the projection and the attention is not launched."""
@@ -351,9 +355,10 @@ class DeviceKernels(KernelSet):
         )
         if not merged:
             return super().qkv_attention(x, weight, bias, step, kv, writes_cache, rotary, num_heads, num_kv_heads,
-                                         head_dim, window, scale, out)
+                                         head_dim, window, scale, out, chunk)
         slices = self.linear_split(x, weight)
         window = int(window) if window else 0
+        chunk = int(chunk) if chunk else 0
         tokens = step.num_tokens
         splits = self.plan_splits(tokens, num_heads, num_kv_heads, step.max_kv_len)
         if splits <= 2 * _CLUSTER_SPLITS:
@@ -371,7 +376,7 @@ class DeviceKernels(KernelSet):
                 out.data_ptr(), out.stride(0), scratch.data_ptr() if scratch is not None else None,
                 step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
                 kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), tokens,
-                num_heads, num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, float(scale), splits,
+                num_heads, num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, chunk, float(scale), splits,
                 self.error_flag.data_ptr(), self._stream(),
             ),
             "attention_decode_mma_qkv",
@@ -379,9 +384,12 @@ class DeviceKernels(KernelSet):
         self._ran("attention_decode_mma", 1 if splits <= _CLUSTER_SPLITS else 2)
         self._ran("attention_decode_mma_qkv", 0)
 
-    def attention(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale) -> None:
+    def attention(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale, chunk=None) -> None:
         window = int(window) if window else 0
-        n_dec = step.num_decode_tokens if head_dim in _DECODE_HEAD_DIMS else 0
+        chunk = int(chunk) if chunk else 0
+        value_dim = kv.v.shape[-1]
+        same = value_dim == head_dim  # every kernel but the size-agnostic one wants values as large as keys
+        n_dec = step.num_decode_tokens if head_dim in _DECODE_HEAD_DIMS and same else 0
         element = qkv.element_size()
         if n_dec > 0:
             splits = self.plan_splits(n_dec, num_heads, num_kv_heads, step.max_kv_len)
@@ -398,7 +406,7 @@ class DeviceKernels(KernelSet):
                 scratch.data_ptr() if scratch is not None else None, step.positions.data_ptr(),
                 step.token_seq.data_ptr(), step.seq_seat.data_ptr(), kv.block_table.data_ptr(),
                 kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), n_dec, num_heads, num_kv_heads,
-                head_dim, kv.page_size, kv.num_pages, window, float(scale), splits,
+                head_dim, kv.page_size, kv.num_pages, window, chunk, float(scale), splits,
             ]
             if tensor_cores:
                 check(
@@ -412,7 +420,8 @@ class DeviceKernels(KernelSet):
                 )
             self._ran("attention_decode_mma" if tensor_cores else "attention_decode", 1 if in_kernel_merge else 2)
         rest = step.num_tokens - n_dec
-        tiled = rest > 0 and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and step.num_q_tiles and n_dec == step.num_decode_tokens
+        tiled = (rest > 0 and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and step.num_q_tiles
+                 and n_dec == step.num_decode_tokens and same and not chunk)
         if tiled and self._attention_tcgen05(qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale):
             pass
         elif tiled:
@@ -434,8 +443,8 @@ class DeviceKernels(KernelSet):
                     out.data_ptr() + n_dec * out.stride(0) * element, out.stride(0),
                     step.positions.data_ptr() + 4 * n_dec, step.token_seq.data_ptr() + 4 * n_dec,
                     step.seq_seat.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[-1],
-                    kv.k.data_ptr(), kv.v.data_ptr(), rest, num_heads, num_kv_heads, head_dim, kv.page_size,
-                    kv.num_pages, window, float(scale), self.code, self.error_flag.data_ptr(), self._stream(),
+                    kv.k.data_ptr(), kv.v.data_ptr(), rest, num_heads, num_kv_heads, head_dim, value_dim, kv.page_size,
+                    kv.num_pages, window, chunk, float(scale), self.code, self.error_flag.data_ptr(), self._stream(),
                 ),
                 "attention_generic",
             )
@@ -455,6 +464,104 @@ class DeviceKernels(KernelSet):
         check(code, "attention_prefill_tcgen05")
         self._ran("attention_prefill_tcgen05")
         return True
+
+    # -- layers with per-request state: layer norm over a pending sum, gates, convolutions, recurrences ---------
+    def add_layernorm(self, delta, residual, weight, bias, eps, out, rows_index=None) -> None:
+        pairs = [] if delta is None else Terms.of(delta).flat()
+        if len(pairs) > _MAX_TERMS:  # more terms than the kernel takes: the tail is summed here, in float32
+            tail = Terms(pairs[_MAX_TERMS - 1 :]).total()
+            pairs = pairs[: _MAX_TERMS - 1] + [(tail, 1.0)]
+        pairs = [(t if t.is_contiguous() else t.contiguous(), s) for t, s in pairs]
+        pointers = (ctypes.c_void_p * max(1, len(pairs)))(*[t.data_ptr() for t, _ in pairs])
+        scales = (ctypes.c_float * max(1, len(pairs)))(*[s for _, s in pairs])
+        check(
+            function("distie_add_layernorm")(
+                pointers, scales, len(pairs), residual.data_ptr(), weight.data_ptr(), bias.data_ptr(), out.data_ptr(),
+                rows_index.data_ptr() if rows_index is not None else None, out.shape[0], residual.shape[1], float(eps),
+                self.code, self._stream(),
+            ),
+            "add_layernorm",
+        )
+        self._ran("add_layernorm")
+
+    @staticmethod
+    def _rows32(x: torch.Tensor, what: str) -> torch.Tensor:
+        if x.dtype != torch.float32 or x.stride(-1) != 1:
+            raise KernelError(f"{what}: a float32 matrix with unit column stride is expected")
+        return x
+
+    def kv_write(self, k, v, step, kv) -> None:
+        if k.dtype != v.dtype or k.dtype not in _CODE or k.stride(1) != 1 or v.stride(1) != 1:
+            raise KernelError("kv_write: keys and values of one float type with unit column stride are expected")
+        check(
+            function("distie_kv_write")(
+                k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), _CODE[k.dtype], step.positions.data_ptr(),
+                step.token_seq.data_ptr(), step.seq_seat.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[-1],
+                kv.k.data_ptr(), kv.v.data_ptr(), step.num_tokens, kv.k.shape[1], kv.k.shape[-1], kv.v.shape[-1],
+                kv.page_size, kv.num_pages, _CODE[kv.k.dtype], self.error_flag.data_ptr(), self._stream(),
+            ),
+            "kv_write",
+        )
+        self._ran("kv_write")
+
+    def head_gate(self, x, logits, num_heads) -> None:
+        self._rows32(logits, "head_gate")
+        if not x.is_contiguous():
+            raise KernelError("head_gate: a contiguous activation is expected")
+        check(
+            function("distie_head_gate")(
+                x.data_ptr(), logits.data_ptr(), logits.stride(0), x.shape[0], num_heads, x.shape[1] // num_heads,
+                _CODE[x.dtype], self._stream(),
+            ),
+            "head_gate",
+        )
+        self._ran("head_gate")
+
+    def short_conv(self, x, weight, bias, state, step, activation="silu"):
+        self._rows32(x, "short_conv")
+        channels, taps = weight.shape
+        out = torch.empty((step.num_tokens, channels), dtype=torch.float32, device=x.device)
+        check(
+            function("distie_short_conv")(
+                x.data_ptr(), x.stride(0), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
+                state.data_ptr() if state is not None else None, step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
+                step.num_tokens, step.num_seqs, channels, taps, int(activation == "silu"), out.data_ptr(), self._stream(),
+            ),
+            "short_conv",
+        )
+        self._ran("short_conv", 2 if taps > 1 else 1)
+        return out
+
+    def linear_recurrence(self, rule, q, k, v, decay, write, state, step, heads, groups, key_dim, value_dim,
+                          decay_rate=None, decay_bias=None, skip=None):
+        for name, t in (("q", q), ("k", k), ("v", v), ("decay", decay), ("write", write)):
+            self._rows32(t, f"linear_recurrence {name}")
+        out = torch.empty((step.num_tokens, heads * value_dim), dtype=torch.float32, device=q.device)
+        check(
+            function("distie_linear_recurrence")(
+                _RULES[rule], q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+                decay.data_ptr(), decay.stride(0), write.data_ptr(), write.stride(0), decay_rate.data_ptr(),
+                decay_bias.data_ptr() if decay_bias is not None else None, skip.data_ptr() if skip is not None else None,
+                state.data_ptr(), out.data_ptr(), out.stride(0), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
+                step.num_tokens, step.num_seqs, heads, groups, key_dim, value_dim, self._stream(),
+            ),
+            "linear_recurrence",
+        )
+        self._ran("linear_recurrence")
+        return out
+
+    def gated_rmsnorm(self, x, gate, weight, eps, group, gate_first, out) -> None:
+        self._rows32(x, "gated_rmsnorm x")
+        self._rows32(gate, "gated_rmsnorm gate")
+        check(
+            function("distie_gated_rmsnorm")(
+                x.data_ptr(), x.stride(0), gate.data_ptr(), gate.stride(0), weight.data_ptr(), weight.numel(),
+                out.data_ptr(), out.stride(0), x.shape[0], x.shape[1], group, float(eps), int(bool(gate_first)),
+                _CODE[out.dtype], self._stream(),
+            ),
+            "gated_rmsnorm",
+        )
+        self._ran("gated_rmsnorm")
 
     def sample(self, logits, temperatures, uniforms, out_tokens) -> None:
         check(

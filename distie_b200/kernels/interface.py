@@ -13,7 +13,11 @@ Shapes (``T`` tokens of this step, ``B`` requests of this step):
     token_ids [T], positions [T], token_seq [T] (batch row of each token),
     seq_seat [B] (seat = row of the block tables and of the state slots).
 ``KvSlot``        one cache slot of one group
-    k, v  [pages, kv_heads, page_size, head_dim]; block_table [seats, width] int32
+    k  [pages, kv_heads, page_size, head_dim], v  [pages, kv_heads, page_size, value_dim];
+    block_table [seats, width] int32
+
+Which keys a token sees: all keys up to its own position (``first_visible``), the last
+``window`` of them, or those of its own ``chunk`` (positions ``chunk * n .. chunk * (n + 1) - 1``).
 """
 
 from __future__ import annotations
@@ -49,6 +53,52 @@ class KvSlot:
     block_table: torch.Tensor
     page_size: int
     num_pages: int
+
+
+def first_visible(position: int, window: int | None = None, chunk: int | None = None) -> int:
+    """The oldest key the token at ``position`` sees (it sees every key from there to itself)."""
+    first = 0
+    if window:
+        first = max(first, position - int(window) + 1)
+    if chunk:
+        first = max(first, position // int(chunk) * int(chunk))
+    return first
+
+
+@dataclass
+class Terms:
+    """A sum that is still to be done: ``sum_i scale_i * tensor_i``, each tensor ``[T, hidden]`` or float32
+    slices ``[S, T, hidden]`` (see :meth:`KernelSet.linear_split`).  A block whose sublayers all read one norm
+    hands its sublayers' outputs over like this, and the norm kernel that follows adds them to the residual."""
+
+    items: list  # of (tensor, scale)
+
+    @classmethod
+    def of(cls, value, scale: float = 1.0) -> "Terms":
+        if isinstance(value, Terms):
+            return cls([(t, s * scale) for t, s in value.items])
+        return cls([(value, float(scale))])
+
+    def __add__(self, other: "Terms") -> "Terms":
+        return Terms(self.items + Terms.of(other).items)
+
+    def flat(self) -> list:
+        """``(float32 [T, hidden] matrix, scale)`` pairs: every slice on its own."""
+        out = []
+        for tensor, scale in self.items:
+            if tensor.dim() == 3:
+                out += [(tensor[i], scale) for i in range(tensor.shape[0])]
+            else:
+                out.append((tensor if tensor.dtype == torch.float32 else tensor.float(), scale))
+        return out
+
+    def total(self) -> torch.Tensor:
+        """The sum itself, float32 ``[T, hidden]``, in the order of the items."""
+        total = None
+        for tensor, scale in self.flat():
+            part = tensor if scale == 1.0 else tensor * scale
+            total = part if total is None else total + part
+        return total
 
 
 @dataclass(frozen=True)
@@ -123,19 +173,69 @@ class KernelSet(ABC):
 
     def qkv_attention(self, x, weight, bias, step: StepTensors, kv: KvSlot, writes_cache: bool,
                       rotary: RotaryTable | None, num_heads: int, num_kv_heads: int, head_dim: int,
-                      window: int | None, scale: float, out) -> None:
+                      window: int | None, scale: float, out, chunk: int | None = None) -> None:
         """From the mixer's input to the attention's output: the q/k/v projection, bias, rotation, the new
         keys and values into their pages (if ``writes_cache``) and attention over the pages into ``out``.
         The default is the ops after one another; a set may merge them for some steps."""
         q = torch.empty((x.shape[0], num_heads * head_dim), dtype=out.dtype, device=x.device)
         self.qkv_rope_write(x, weight, bias, step, kv if writes_cache else None, rotary, num_heads, num_kv_heads,
                             head_dim, q)
-        self.attention(q, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale)
+        self.attention(q, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale, chunk)
 
     @abstractmethod
     def attention(self, qkv, out, step: StepTensors, kv: KvSlot, num_heads: int, num_kv_heads: int,
-                  head_dim: int, window: int | None, scale: float) -> None:
-        """Causal (optionally windowed) attention of every token over its request's pages."""
+                  head_dim: int, window: int | None, scale: float, chunk: int | None = None) -> None:
+        """Causal attention of every token over its request's pages, optionally only over the last
+        ``window`` keys or over the keys of the token's own ``chunk``.  The size of a value is the last
+        dimension of ``kv.v`` and may differ from ``head_dim``; ``out`` is ``[T, heads * value size]``."""
+
+    # -- layer norm, gates, short convolutions and linear recurrences (layers with per-request state) --------
+    def add_layernorm(self, delta, residual, weight, bias, eps: float, out, rows_index=None) -> None:
+        """residual += delta (float32, kept); out = (residual - mean) / sqrt(var + eps) * weight + bias, with the
+        variance the mean of the squared deviations.  ``delta``: None, ``[T, hidden]``, float32 slices
+        ``[S, T, hidden]`` or :class:`Terms`.  With ``rows_index`` only those rows, residual kept."""
+        raise NotImplementedError
+
+    def kv_write(self, k, v, step: StepTensors, kv: KvSlot) -> None:
+        """Store the new tokens' keys ``[T, kv_heads * head_dim]`` and values ``[T, kv_heads * value_dim]``
+        (any float type, any row stride) in their pages: the write of layers that rotate nothing."""
+        raise NotImplementedError
+
+    def head_gate(self, x, logits, num_heads: int) -> None:
+        """x ``[T, heads * d]`` in place: head h of token t times sigmoid(logits[t, h]) (float32 logits)."""
+        raise NotImplementedError
+
+    def short_conv(self, x, weight, bias, state, step: StepTensors, activation: str = "silu"):
+        """Causal convolution over time, per channel and per request: ``x [T, C]`` float32 (any row stride),
+        ``weight [C, taps]`` whose last column multiplies the current token, ``state [seats, taps - 1, C]`` the
+        request's last inputs (oldest first; zeros at a request's start), which the call moves on by the
+        step's tokens.  Returns float32 ``[T, C]`` after the activation (``"silu"`` or ``"none"``)."""
+        raise NotImplementedError
+
+    def linear_recurrence(self, rule: str, q, k, v, decay, write, state, step: StepTensors, heads: int, groups: int,
+                          key_dim: int, value_dim: int, decay_rate=None, decay_bias=None, skip=None):
+        """A matrix state ``S [key_dim, value_dim]`` per head and request, moved on token by token in float32:
+
+        ``S <- g S;  u = write-term;  S <- S + k u^T;  o = S^T q (+ skip * v)``
+
+        Head h reads q and k of group ``h // (heads / groups)``.  ``q, k [T, groups * key_dim]``,
+        ``v [T, heads * value_dim]``, ``decay, write [T, heads]``, all float32 with any row stride.
+
+        ``rule="delta"``: q and k are made unit vectors per head first (``x / sqrt(sum x^2 + 1e-6)``, q also
+        times ``key_dim**-0.5``); ``g = exp(-exp(decay_rate) * softplus(decay + decay_bias))``;
+        ``u = sigmoid(write) * (v - S^T k)`` with the decayed S.
+        ``rule="ssd"``: ``dt = softplus(write + decay_bias)``; ``g = exp(-exp(decay_rate) * dt)``; ``u = dt * v``;
+        ``skip [heads]`` adds ``skip_h * v`` to the read-out (``decay`` is not read).
+
+        ``state`` is ``[seats, heads, value_dim, key_dim]`` float32 (S transposed), read and written through
+        each token's seat.  Returns float32 ``[T, heads * value_dim]``."""
+        raise NotImplementedError
+
+    def gated_rmsnorm(self, x, gate, weight, eps: float, group: int, gate_first: bool, out) -> None:
+        """Root-mean-square norm over groups of ``group`` neighbouring columns of ``x [T, n]`` (float32) with
+        a SiLU gate: ``gate_first``: ``norm(x * silu(gate)) * weight``; else ``norm(x) * weight * silu(gate)``.
+        ``weight`` is float32 of ``n`` elements, or fewer, then repeated (``weight[column % len]``)."""
+        raise NotImplementedError
 
     @abstractmethod
     def sample(self, logits, temperatures, uniforms, out_tokens) -> None:

@@ -30,8 +30,8 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     ),
     "distie_rope_rows": ("base", [P, P, P, P, I, P, F, I, I, I, I, I, P, P, P, P]),
     "distie_bias_cast": ("base", [P, P, P, L, I, I, P]),
-    "distie_attention_generic": ("base", [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P, P]),
-    "distie_attention_decode": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, I, P, P]),
+    "distie_attention_generic": ("base", [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P]),
+    "distie_attention_decode": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P]),
     "distie_attention_decode_scratch_floats": ("base", [I, I, I, I]),
     "distie_sample": ("base", [P, L, I, I, P, P, P, P]),
     "distie_attention_prefill": ("bf16", [P, I, P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, P]),
@@ -40,10 +40,18 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
         "bf16", [P, I, P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, P, P]
     ),
     "distie_attention_decode_mma_stages": ("bf16", [I, I, I, I]),
-    "distie_attention_decode_mma": ("bf16", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P, P]),
+    "distie_attention_decode_mma": ("bf16", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, I, P, P]),
     "distie_attention_decode_mma_qkv": (
-        "bf16", [P, I, L, I, P, P, F, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P, P]
+        "bf16", [P, I, L, I, P, P, F, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, I, P, P]
     ),
+    "distie_add_layernorm": ("state", [P, P, I, P, P, P, P, P, I, I, F, I, P]),
+    "distie_kv_write": ("state", [P, I, P, I, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P, P]),
+    "distie_head_gate": ("state", [P, P, I, I, I, I, I, P]),
+    "distie_short_conv": ("state", [P, I, P, P, P, P, P, I, I, I, I, I, P, P]),
+    "distie_linear_recurrence": (
+        "state", [I, P, I, P, I, P, I, P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, P]
+    ),
+    "distie_gated_rmsnorm": ("state", [P, I, P, I, P, I, P, I, I, I, I, F, I, I, P]),
     "distie_gemm_tcgen05": ("bf16", [P, I, P, P, I, I, I, I, I, I, I, P, P]),
     "distie_gemm_tcgen05_qkv": ("bf16", [P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P]),
     "distie_gemm_tcgen05_skinny_splits": ("bf16", [I, I, I]),

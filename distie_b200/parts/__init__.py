@@ -15,7 +15,7 @@ from .base import (
     TensorSpec,
     build_part,
 )
-from . import attention, block, mlp, norm, position  # noqa: F401  (register the built-in kinds)
+from . import attention, block, hybrid, mlp, norm, position, recurrent  # noqa: F401  (register the built-in kinds)
 
 __all__ = [
     "BLOCKS",

@@ -7,6 +7,12 @@ in their pages before anything is read (worker/src/inference/qwen2/paged_attn.py
 by ``head_dim**-0.5``; a token at position ``p`` sees keys ``<= p`` (and, with a
 window ``w``, ``> p - w``); softmax in float32; output projection.
 
+Beyond the reference: ``chunk`` (a token sees only the keys of its own chunk of that many
+positions, counted from position 0 of the request), ``value_dim`` (values of another size than
+keys), ``gate="head_sigmoid"`` (a projection ``g`` of the mixer's input to one number per head;
+head h's output is multiplied by ``sigmoid(g_h)`` before the output projection) and ``names`` (what
+the tensors are called in the checkpoint).
+
 The three projections are one product against the row-stacked weight; rotation
 and cache write are one kernel; attention reads q from the same buffer.
 """
@@ -23,21 +29,36 @@ from .linear import Linear, fuse_rows
 @MIXERS.register("gqa_attention")
 class GqaAttention:
     """params: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``qkv_bias``, ``out_bias``,
-    ``window`` (None: full), ``scale`` (None: ``head_dim**-0.5``), ``position`` (a PartSpec).
+    ``window`` (None: full), ``chunk`` (None: none), ``value_dim`` (None: ``head_dim``), ``gate`` (None or
+    ``"head_sigmoid"``), ``scale`` (None: ``head_dim**-0.5``), ``position`` (a PartSpec), ``names``.
 
-    tensors: ``q_proj``/``k_proj``/``v_proj``/``o_proj`` ``.weight`` (and ``.bias``).
+    tensors: ``q_proj``/``k_proj``/``v_proj``/``o_proj`` ``.weight`` (and ``.bias``), ``g_proj.weight`` with a
+    gate; ``names`` maps ``q, k, v, o, g`` to other names (biases then add ``.bias`` to the stem).
     """
 
-    def __init__(self, qkv: Linear, out: Linear, position, params: dict, kernels) -> None:
+    _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+              "g": "g_proj.weight"}
+
+    def __init__(self, qkv: Linear, out: Linear, position, params: dict, kernels, gate: Linear | None = None) -> None:
         self.qkv = qkv
         self.out = out
+        self.gate = gate
         self.position = position
         self.num_heads = int(params["num_heads"])
         self.num_kv_heads = int(params["num_kv_heads"])
         self.head_dim = int(params["head_dim"])
+        self.value_dim = int(params.get("value_dim") or self.head_dim)
         self.window = params.get("window")
+        self.chunk = params.get("chunk")
         self.scale = float(params.get("scale") or self.head_dim**-0.5)
         self.kernels = kernels
+
+    @classmethod
+    def _name(cls, spec: PartSpec, which: str, bias: bool = False) -> str:
+        name = spec.prefix + spec.params.get("names", cls._NAMES).get(which, cls._NAMES[which])
+        if not bias:
+            return name
+        return (name[: -len(".weight")] if name.endswith(".weight") else name) + ".bias"
 
     # -- declarations -------------------------------------------------------
     @staticmethod
@@ -45,38 +66,47 @@ class GqaAttention:
         heads, kv_heads, dim = int(params["num_heads"]), int(params["num_kv_heads"]), int(params["head_dim"])
         if heads < 1 or kv_heads < 1 or heads % kv_heads:
             raise ValueError(f"num_heads ({heads}) must be a positive multiple of num_kv_heads ({kv_heads})")
-        if dim < 16 or dim % 16 or dim > 256:
-            raise ValueError(f"head_dim {dim}: the attention kernels take multiples of 16 from 16 to 256")
-        window = params.get("window")
-        if window is not None and int(window) < 1:
-            raise ValueError(f"window must be >= 1, got {window}")
+        vdim = int(params.get("value_dim") or dim)
+        if dim < 1 or dim > 256 or vdim < 1 or vdim > 256:
+            raise ValueError(f"head_dim {dim} / value_dim {vdim}: the attention kernels take 1 to 256")
+        for key in ("window", "chunk"):
+            if params.get(key) is not None and int(params[key]) < 1:
+                raise ValueError(f"{key} must be >= 1, got {params[key]}")
+        if params.get("gate") not in (None, "head_sigmoid"):
+            raise ValueError(f"gate {params['gate']!r}: None or 'head_sigmoid'")
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, hidden_size: int) -> list[TensorSpec]:
         cls._check(spec.params)
-        p, prm = spec.prefix, spec.params
+        prm = spec.params
+        vdim = int(prm.get("value_dim") or prm["head_dim"])
         q_out = prm["num_heads"] * prm["head_dim"]
         kv_out = prm["num_kv_heads"] * prm["head_dim"]
+        v_out = prm["num_kv_heads"] * vdim
         specs = [
-            TensorSpec(p + "q_proj.weight", (q_out, hidden_size)),
-            TensorSpec(p + "k_proj.weight", (kv_out, hidden_size)),
-            TensorSpec(p + "v_proj.weight", (kv_out, hidden_size)),
-            TensorSpec(p + "o_proj.weight", (hidden_size, q_out)),
+            TensorSpec(cls._name(spec, "q"), (q_out, hidden_size)),
+            TensorSpec(cls._name(spec, "k"), (kv_out, hidden_size)),
+            TensorSpec(cls._name(spec, "v"), (v_out, hidden_size)),
         ]
+        if prm.get("gate"):
+            specs.append(TensorSpec(cls._name(spec, "g"), (prm["num_heads"], hidden_size)))
+        specs.append(TensorSpec(cls._name(spec, "o"), (hidden_size, prm["num_heads"] * vdim)))
         if prm.get("qkv_bias", False):
             specs += [
-                TensorSpec(p + "q_proj.bias", (q_out,), "bias"),
-                TensorSpec(p + "k_proj.bias", (kv_out,), "bias"),
-                TensorSpec(p + "v_proj.bias", (kv_out,), "bias"),
+                TensorSpec(cls._name(spec, "q", True), (q_out,), "bias"),
+                TensorSpec(cls._name(spec, "k", True), (kv_out,), "bias"),
+                TensorSpec(cls._name(spec, "v", True), (v_out,), "bias"),
             ]
         if prm.get("out_bias", False):
-            specs.append(TensorSpec(p + "o_proj.bias", (hidden_size,), "bias"))
+            specs.append(TensorSpec(cls._name(spec, "o", True), (hidden_size,), "bias"))
         return specs
 
     @classmethod
     def cache_need(cls, spec: PartSpec) -> CacheNeed:
         prm = spec.params
-        return CacheNeed(int(prm["num_kv_heads"]), int(prm["head_dim"]), prm.get("window"))
+        vdim = int(prm.get("value_dim") or prm["head_dim"])
+        return CacheNeed(int(prm["num_kv_heads"]), int(prm["head_dim"]), prm.get("window"), prm.get("chunk"),
+                         vdim if vdim != int(prm["head_dim"]) else None)
 
     @classmethod
     def state_need(cls, spec: PartSpec):
@@ -85,17 +115,19 @@ class GqaAttention:
     @classmethod
     def build(cls, spec: PartSpec, ctx: BuildContext) -> "GqaAttention":
         cls._check(spec.params)
-        p, prm, w = spec.prefix, spec.params, ctx.weights
-        weight = fuse_rows([w.matrix(p + f"{n}_proj.weight") for n in "qkv"])
-        bias = fuse_rows([w.vector(p + f"{n}_proj.bias") for n in "qkv"]) if prm.get("qkv_bias", False) else None
-        out_bias = w.vector(p + "o_proj.bias") if prm.get("out_bias", False) else None
-        position = build_part(POSITION_ENCODINGS, prm["position"], ctx)
+        prm, w = spec.params, ctx.weights
+        weight = fuse_rows([w.matrix(cls._name(spec, n)) for n in "qkv"])
+        bias = fuse_rows([w.vector(cls._name(spec, n, True)) for n in "qkv"]) if prm.get("qkv_bias", False) else None
+        out_bias = w.vector(cls._name(spec, "o", True)) if prm.get("out_bias", False) else None
+        position = build_part(POSITION_ENCODINGS, prm.get("position") or PartSpec("none"), ctx)
+        gate = Linear(w.matrix(cls._name(spec, "g")), None, ctx.kernels) if prm.get("gate") else None
         return cls(
             Linear(weight, bias, ctx.kernels),
-            Linear(w.matrix(p + "o_proj.weight"), out_bias, ctx.kernels),
+            Linear(w.matrix(cls._name(spec, "o")), out_bias, ctx.kernels),
             position,
             dict(prm),
             ctx.kernels,
+            gate,
         )
 
     # -- the step -----------------------------------------------------------
@@ -103,9 +135,22 @@ class GqaAttention:
         if run.kv is None:
             raise RuntimeError("attention needs a cache slot")
         k = self.kernels
-        mixed = torch.empty((x.shape[0], self.num_heads * self.head_dim), dtype=x.dtype, device=x.device)
+        mixed = torch.empty((x.shape[0], self.num_heads * self.value_dim), dtype=x.dtype, device=x.device)
         table = self.position.rotary_table()
-        if table is None and hasattr(self.position, "apply"):
+        if self.value_dim != self.head_dim:
+            # Values of another size than keys: nothing of the fused kernels fits; the projection is finished,
+            # keys and values go to their pages as they are (such layers rotate nothing) and the size-agnostic
+            # attention reads q from the projection's first columns.
+            if table is not None or hasattr(self.position, "apply"):
+                raise RuntimeError("a value size that differs from the key size goes with no rotation only")
+            qkv = k.linear(x, self.qkv.weight, self.qkv.bias)
+            q_end = self.num_heads * self.head_dim
+            k_end = q_end + self.num_kv_heads * self.head_dim
+            if run.writes_cache:
+                k.kv_write(qkv[:, q_end:k_end], qkv[:, k_end:], run.step, run.kv)
+            k.attention(qkv, mixed, run.step, run.kv, self.num_heads, self.num_kv_heads, self.head_dim, self.window,
+                        self.scale, self.chunk)
+        elif table is None and hasattr(self.position, "apply"):
             # An encoding of its own: the projection is finished here, the encoding changes q and k in
             # place, and the fused kernel only stores k and v and copies q out.
             q = torch.empty_like(mixed)
@@ -113,12 +158,15 @@ class GqaAttention:
             self.position.apply(qkv, run.step, self.num_heads, self.num_kv_heads, self.head_dim)
             k.rope_kv_write(qkv, run.step, run.kv if run.writes_cache else None, None, self.num_heads,
                             self.num_kv_heads, self.head_dim, q_out=q)
-            k.attention(q, mixed, run.step, run.kv, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale)
+            k.attention(q, mixed, run.step, run.kv, self.num_heads, self.num_kv_heads, self.head_dim, self.window,
+                        self.scale, self.chunk)
         else:
             # The projection, the bias, the rotation of q and k, the store of k and v in their pages and the
             # attention over the pages as one op of the kernel set, which may merge kernels for some steps.
             k.qkv_attention(x, self.qkv.weight, self.qkv.bias, run.step, run.kv, run.writes_cache, table,
-                            self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale, mixed)
+                            self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale, mixed, self.chunk)
+        if self.gate is not None:
+            k.head_gate(mixed, k.linear(x, self.gate.weight, None, torch.float32), self.num_heads)
         if self.out.bias is not None:
             return self.out(mixed)
         return k.linear_split(mixed, self.out.weight)  # summed by the norm that follows

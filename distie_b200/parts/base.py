@@ -18,8 +18,9 @@ block          ``tensor_specs``, ``build``, ``forward(stream, run)``
 
 ``forward`` of a mixer or feed-forward takes the normalised activations ``[T,
 hidden]`` of the step's tokens and returns what is to be added to the residual
-stream: ``[T, hidden]``, or float32 slices ``[S, T, hidden]`` whose sum it is (what
-``KernelSet.linear_split`` returns; the norm that follows adds them up).  The :class:`LayerRun` tells a mixer everything about the step: the
+stream: ``[T, hidden]``, float32 slices ``[S, T, hidden]`` whose sum it is (what
+``KernelSet.linear_split`` returns; the norm that follows adds them up), or
+:class:`~distie_b200.kernels.interface.Terms`, a weighted sum of such tensors.  The :class:`LayerRun` tells a mixer everything about the step: the
 tokens' positions and requests, its cache slot and its per-request state.
 """
 
@@ -31,7 +32,7 @@ from typing import Any, Callable, Sequence
 import torch
 
 from ..config.model_spec import PartSpec
-from ..kernels.interface import KernelSet, KvSlot, StepTensors
+from ..kernels.interface import KernelSet, KvSlot, StepTensors, Terms
 
 
 # -- what parts declare --------------------------------------------------------
@@ -57,11 +58,21 @@ class CacheNeed:
     num_kv_heads: int
     head_dim: int
     window: int | None = None  # None: every key is kept; n: only the last n positions are read
+    chunk: int | None = None   # n: a token reads only keys of its own chunk of n positions (counted from 0)
+    value_dim: int | None = None  # size of a value when it differs from head_dim
+
+    @property
+    def v_dim(self) -> int:
+        return int(self.value_dim or self.head_dim)
 
 
 @dataclass(frozen=True)
 class StateNeed:
-    """State of fixed size per request (one slot per seat), zeroed when a request starts."""
+    """State of fixed size per request (one slot per seat), zeroed when a request starts.
+
+    A mixer's ``state_need`` returns one of these, or a dict of them by name when it keeps several
+    tensors (a matrix state and the last inputs of a short convolution, say); ``LayerRun.state`` is then
+    a dict of tensors under the same names."""
 
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
@@ -100,7 +111,7 @@ class LayerRun:
     step: StepTensors
     seqs: Sequence[SeqSlice]
     kv: KvSlot | None = None
-    state: torch.Tensor | None = None  # [seats, *StateNeed.shape] of this call's slot
+    state: Any = None  # [seats, *StateNeed.shape] of this call's slot, or a dict of such tensors by name
     writes_cache: bool = True
     extras: dict = field(default_factory=dict)
 
@@ -119,7 +130,10 @@ class ResidualStream:
 
     def settle(self) -> torch.Tensor:
         if self.pending is not None:
-            delta = self.pending.sum(0) if self.pending.dim() == 3 else self.pending  # slices of a split product
+            if isinstance(self.pending, Terms):
+                delta = self.pending.total()
+            else:
+                delta = self.pending.sum(0) if self.pending.dim() == 3 else self.pending  # slices of a split product
             self.residual.add_(delta.to(torch.float32))
             self.pending = None
         return self.residual

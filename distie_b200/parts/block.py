@@ -4,6 +4,10 @@
 247-249): ``h += mixer(norm_in(h))``; ``h += ff(norm_post(h))``.  The sums are
 float32 and are done by the norm kernel that follows them, so a block leaves its
 feed-forward output pending on the stream.
+
+``parallel``: one norm, and mixer and feed-forward both read its output:
+``h += mixer(norm(h)) + ff(norm(h))``.  Both outputs stay pending as one weighted sum, which the
+next block's norm kernel adds to the float32 residual.
 """
 
 from __future__ import annotations
@@ -11,6 +15,7 @@ from __future__ import annotations
 import torch
 
 from ..config.model_spec import LayerSpec
+from ..kernels.interface import Terms
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildContext, LayerRun, ResidualStream, TensorSpec, build_part
 
 
@@ -56,3 +61,43 @@ class PreNormBlock:
         mixed = self.mixer.forward(x, run)
         self.norm_post.apply(mixed, residual, x)
         stream.pending = self.feed_forward.forward(x, run)
+
+
+@BLOCKS.register("parallel")
+class ParallelBlock:
+    """norms: ``input`` only.  A feed-forward of kind ``none`` adds nothing."""
+
+    def __init__(self, norm_in, mixer, feed_forward, dtype) -> None:
+        self.norm_in = norm_in
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.dtype = dtype
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(part, "graph_safe", True) for part in (self.mixer, self.feed_forward))
+
+    @classmethod
+    def tensor_specs(cls, layer: LayerSpec, hidden_size: int) -> list[TensorSpec]:
+        return (
+            NORMS.get(layer.norms["input"].kind).tensor_specs(layer.norms["input"], hidden_size)
+            + MIXERS.get(layer.mixer.kind).tensor_specs(layer.mixer, hidden_size)
+            + FEED_FORWARDS.get(layer.feed_forward.kind).tensor_specs(layer.feed_forward, hidden_size)
+        )
+
+    @classmethod
+    def build(cls, layer: LayerSpec, ctx: BuildContext) -> "ParallelBlock":
+        return cls(
+            build_part(NORMS, layer.norms["input"], ctx),
+            build_part(MIXERS, layer.mixer, ctx),
+            build_part(FEED_FORWARDS, layer.feed_forward, ctx),
+            ctx.dtype,
+        )
+
+    def forward(self, stream: ResidualStream, run: LayerRun) -> None:
+        residual = stream.residual
+        x = torch.empty(residual.shape, dtype=self.dtype, device=residual.device)
+        self.norm_in.apply(stream.pending, residual, x)
+        pending = Terms.of(self.mixer.forward(x, run))
+        fed = self.feed_forward.forward(x, run)
+        stream.pending = pending if fed is None else pending + Terms.of(fed)
