@@ -188,6 +188,115 @@ def build_engine(shape: dict, layers: int, max_seqs: int, num_blocks: int | None
     return Engine.assemble(arch, typed, source, kernels, config)
 
 
+def build_engine_of(raw: dict, max_seqs: int, num_blocks: int, max_model_len: int, dtype: str = "bfloat16"):
+    """An engine for any registered architecture from its ``config.json`` keys, random weights made on the device."""
+    import torch
+
+    from distie_b200.config import EngineConfig, architecture_of
+    from distie_b200.engine.engine import Engine
+    from distie_b200.kernels import make_kernels
+    from distie_b200.models import model_tensor_specs
+    from distie_b200.weights import RandomSource
+
+    torch_dtype = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    arch = architecture_of(raw)
+    typed = arch.config_cls.from_dict(raw)
+    kernels = make_kernels(torch_dtype, "cuda:0")
+    source = RandomSource(model_tensor_specs(arch.recipe(typed)), seed=0, std=0.02, dtype=torch_dtype, device="cuda:0")
+    config = EngineConfig(num_blocks=num_blocks, page_size=PAGE, max_seqs=max_seqs, token_budget=2048,
+                          max_model_len=max_model_len, dtype=dtype, decode_graphs=True, device="cuda:0")
+    return Engine.assemble(arch, typed, source, kernels, config)
+
+
+# Layer sizes at which the Zelasun design is timed beside the Qwen2 decoder: the width, feed-forward and
+# attention heads of the Qwen2.5-1.5B and -7B layers; the recurrences get as many heads of 128 as the attention
+# (gated delta rule) or twice the width in heads of 128 (Mamba-2), states of 128.
+COMPARE_SIZES = {
+    "1.5b": {"width": 1536, "ff": 8960, "heads": 12, "kv_heads": 2},
+    "7b": {"width": 3584, "ff": 18944, "heads": 28, "kv_heads": 4},
+}
+COMPARE_VOCAB = 32000
+
+
+def zelasun_config(size: dict, layers: int, chunk: int) -> dict:
+    heads, kv = size["heads"], size["kv_heads"]
+    parallel = {
+        "type": "parallel", "mlp": {"kind": "dense", "ff": size["ff"]},
+        "mixer": {
+            "left": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": chunk}},
+            "right": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "conv": 4},
+            "left_scale": 0.5, "right_scale": 0.5,
+        },
+    }
+    mamba = {"type": "mamba2", "mlp": {"kind": "dense", "ff": size["ff"]},
+             "mixer": {"heads": 2 * size["width"] // 128, "vdim": 128, "state": 128, "groups": 2, "norm_groups": 2, "conv": 4}}
+    pattern = [parallel, mamba, mamba, parallel]
+    return {"architecture": "Zelasun", "vocab": COMPARE_VOCAB, "width": size["width"], "norm": {"eps": 1e-5},
+            "layers": [pattern[i % 4] for i in range(layers)]}
+
+
+def qwen2_config(size: dict, layers: int) -> dict:
+    return {"architectures": ["Qwen2ForCausalLM"], "vocab_size": COMPARE_VOCAB, "hidden_size": size["width"],
+            "intermediate_size": size["ff"], "num_hidden_layers": layers, "num_attention_heads": size["heads"],
+            "num_key_value_heads": size["kv_heads"], "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
+            "tie_word_embeddings": True, "max_position_embeddings": 32768}
+
+
+def compare_designs(args) -> int:
+    """``--compare zelasun``: prefill of 2,048 tokens and decode steps at batch ``--batch`` behind 1,024-token prompts,
+    for the Zelasun design and the Qwen2 decoder at equal width, feed-forward, heads and depth.  Each model is
+    built at two depths (4 and 8 layers) so that the time of a layer is the difference, free of embedding and head.
+    One JSON line; not the repository's headline metric."""
+    import gc
+
+    import torch
+
+    from distie_b200.engine.measure import DecodeBurst
+
+    names = [args.shape] if args.shape in COMPARE_SIZES and args.shape != "1.5b" else list(COMPARE_SIZES)
+    if args.only_size:
+        names = [args.only_size]
+    dtype = "bfloat16" if args.dtype == "bf16" else "float32"
+    depths = (4, 8) if args.layers is None else (args.layers,)
+    out = {"compare": "zelasun beside qwen2", "dtype": args.dtype, "batch": args.batch, "prompt_len": PROMPT_LEN,
+           "prefill_tokens": PREFILL_TOKENS, "chunk": args.chunk, "sizes": {}}
+    pages = 64 * -(-(PROMPT_LEN + args.warmup + args.steps + 2 * 64 + 16) // PAGE) + 2 * (PREFILL_TOKENS // PAGE)
+    with ClockSampler() as sampler:
+        for name in names:
+            size = COMPARE_SIZES[name]
+            rows = {}
+            for design in ("zelasun", "qwen2"):
+                point = {}
+                for depth in depths:
+                    raw = zelasun_config(size, depth, args.chunk) if design == "zelasun" else qwen2_config(size, depth)
+                    engine = build_engine_of(raw, 64, pages, CONTEXT, dtype)
+                    burst = DecodeBurst(engine.runner, state_may_repeat=True)
+                    entry = {}
+                    if args.only in (None, "prefill"):
+                        entry["prefill_ms"] = round(time_prefill(engine, repeats=3)["ms"], 3)
+                    if args.only in (None, "decode"):
+                        decode = time_decode(engine, burst, args.batch, PROMPT_LEN, args.steps, args.warmup)
+                        entry["decode_ms_per_step"] = round(decode["ms_per_step"], 4)
+                        entry["decode_launches_per_step"] = decode["launches"] // args.steps
+                    entry["weight_mb"] = round(engine.model.weight_bytes() / 1e6, 1)
+                    entry["kernels"] = dict(sorted(engine.model.kernels.kernel_counts.items()))
+                    point[depth] = entry
+                    del engine, burst
+                    gc.collect()
+                    torch.cuda.empty_cache()
+                if len(depths) == 2:
+                    lo, hi = depths
+                    span = hi - lo
+                    per_layer = {k: round((point[hi][k] - point[lo][k]) / span, 4)
+                                 for k in ("prefill_ms", "decode_ms_per_step", "weight_mb") if k in point[lo]}
+                    point["per_layer"] = per_layer
+                rows[design] = point
+            out["sizes"][name] = rows
+    out["clocks"] = sampler.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def random_prompt(vocab: int, length: int, seed: int) -> list[int]:
     import torch
 
@@ -406,6 +515,10 @@ def main() -> int:
     parser.add_argument("--ref-attn", default=None, choices=["auto", "flash", "torch"],
                         help="with --impl reference: its attention backend (default: DISTIE_ATTN, else auto)")
     parser.add_argument("--ref-device", default=None, help=argparse.SUPPRESS)  # "cpu": a dry run of the reference arm
+    parser.add_argument("--compare", default=None, choices=["zelasun"],
+                        help="time another design beside the Qwen2 decoder at equal layer sizes instead of the default run")
+    parser.add_argument("--chunk", type=int, default=1024, help="with --compare: the chunk of the design's attention")
+    parser.add_argument("--only-size", default=None, choices=["1.5b", "7b"], help="with --compare: one of the sizes")
     args = parser.parse_args()
     if args.gpus != 1:
         print(json.dumps({"unsupported": f"--gpus {args.gpus}: this engine runs on one GPU; run with --gpus 1", "n_gpus": args.gpus}))
@@ -414,6 +527,8 @@ def main() -> int:
         args.warmup = 3
     if args.impl == "reference":
         return reference_arm(args)
+    if args.compare:
+        return compare_designs(args)
 
     from distie_b200.engine.measure import DecodeBurst
 

@@ -65,7 +65,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
                          const int* __restrict__ block_table, int table_width,
                          const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                          int group_size, int num_kv_heads, int page_size, int page_shift, int num_pages,
-                         int window, float scale_log2, int* __restrict__ error) {
+                         int window, int key_chunk, float scale_log2, int* __restrict__ error) {
   constexpr int CHUNKS = D / 8;                       // 16-byte chunks per row
   constexpr int TILE_BYTES = kTileN * D * 2;
   constexpr int ROWS_PER_PASS = kPrefillWarps * 32 / CHUNKS;
@@ -89,7 +89,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
   const int seat = seq_seat[token_seq[t0]];
   const int* table = block_table + (size_t)seat * table_width;
   const int p_last = p0 + rows - 1;
-  const int first_key = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+  const int first_key = first_visible_key(p0, window, key_chunk);
   const int kb_start = (first_key / kTileN) * kTileN;
   const int num_blocks = (p_last - kb_start) / kTileN + 1;
 
@@ -186,7 +186,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
     // its first key is inside the window of the warp's last row.
     const int kb = kb_start + block * kTileN;
     const int warp_first = p0 + warp * 16, warp_last = warp_first + 15;
-    const bool whole = kb + kTileN - 1 <= warp_first && (window <= 0 || kb > warp_last - window);
+    const bool whole = kb + kTileN - 1 <= warp_first && kb >= first_visible_key(warp_last, window, key_chunk);
     float tile_max[2] = {-INFINITY, -INFINITY};
     if (whole) {
 #pragma unroll
@@ -200,7 +200,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
         for (int r = 0; r < 4; ++r) {
           const int key = kb + i * 8 + 2 * c + (r & 1);
           const int p = pos_row[r >> 1];
-          const bool seen = key <= p && (window <= 0 || key > p - window);
+          const bool seen = key <= p && key >= first_visible_key(p, window, key_chunk);
           s[i][r] = seen ? s[i][r] : -INFINITY;
           tile_max[r >> 1] = fmaxf(tile_max[r >> 1], s[i][r]);
         }
@@ -277,7 +277,7 @@ template <int D>
 int launch_prefill(const void* q, int q_row_stride, void* out, int out_row_stride, const int* q_tiles, int num_tiles,
                    const int* positions, const int* token_seq, const int* seq_seat, const int* block_table,
                    int table_width, const void* k_cache, const void* v_cache, int num_heads, int num_kv_heads,
-                   int page_size, int num_pages, int window, float scale, int* error, cudaStream_t stream) {
+                   int page_size, int num_pages, int window, int key_chunk, float scale, int* error, cudaStream_t stream) {
   const int shared = 4 * kTileN * D * 2;
   static bool configured = false;
   if (!configured) {
@@ -293,7 +293,7 @@ int launch_prefill(const void* q, int q_row_stride, void* out, int out_row_strid
   attention_prefill_kernel<D><<<grid, kPrefillWarps * 32, shared, stream>>>(
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, q_tiles, positions, token_seq,
       seq_seat, block_table, table_width, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-      num_heads / num_kv_heads, num_kv_heads, page_size, page_shift, num_pages, window,
+      num_heads / num_kv_heads, num_kv_heads, page_size, page_shift, num_pages, window, key_chunk,
       scale * 1.4426950408889634f, error);
   DISTIE_LAUNCH_CHECK();
   return 0;
@@ -310,7 +310,7 @@ extern "C" int distie_attention_prefill(const void* q, int q_row_stride, void* o
                                         const int* q_tiles, int num_tiles, const int* positions,
                                         const int* token_seq, const int* seq_seat, const int* block_table,
                                         int table_width, const void* k_cache, const void* v_cache, int num_heads,
-                                        int num_kv_heads, int head_dim, int page_size, int num_pages, int window,
+                                        int num_kv_heads, int head_dim, int page_size, int num_pages, int window, int key_chunk,
                                         float scale, int* error, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
@@ -319,7 +319,7 @@ extern "C" int distie_attention_prefill(const void* q, int q_row_stride, void* o
 #define DISTIE_PREFILL(DV)                                                                                        \
   return launch_prefill<DV>(q, q_row_stride, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,       \
                             seq_seat, block_table, table_width, k_cache, v_cache, num_heads, num_kv_heads,        \
-                            page_size, num_pages, window, scale, error, stream)
+                            page_size, num_pages, window, key_chunk, scale, error, stream)
   switch (head_dim) {
     case 64: DISTIE_PREFILL(64);
     case 128: DISTIE_PREFILL(128);

@@ -117,7 +117,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  const int* __restrict__ positions, const int* __restrict__ token_seq,
                                  const int* __restrict__ seq_seat, const int* __restrict__ block_table,
                                  int table_width, int group_size, int num_kv_heads, int page_shift, int num_pages,
-                                 int window, float scale_log2, int* __restrict__ error) {
+                                 int window, int key_chunk, float scale_log2, int* __restrict__ error) {
   extern __shared__ unsigned char raw[];
   auto& sm = *reinterpret_cast<AttnShared<D>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   constexpr int HALVES = D / 64;
@@ -177,7 +177,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int pos0 = positions[t0];
   const int seat = seq_seat[token_seq[t0]];
   const int last_pos = pos0 + rows - 1;
-  const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int first_key = first_visible_key(pos0, window, key_chunk);
   const int block_first = first_key / kAttnKeys;
   const int blocks = last_pos / kAttnKeys - block_first + 1;
   const int page_size = 1 << page_shift;
@@ -296,7 +296,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const uint32_t lane_base = tmem + ((uint32_t)(quadrant * 32) << 16);
     const uint32_t o_addr = lane_base + O_COL + g * D;
     const int limit = min(pos0 + r, last_pos);                      // newest key this row may see
-    const int oldest = window > 0 ? pos0 + r - window + 1 : 0;      // oldest key inside its window
+    const int oldest = first_visible_key(limit, window, key_chunk);  // oldest key inside its window or chunk
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     // One lane polls the barrier; the warp continues as one (the tensor-memory instructions need all lanes).
@@ -316,7 +316,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // No row of the tile needs a mask when every key of the block is old enough and inside every window.
       const bool unmasked =
-          block_key0 + kAttnKeys - 1 <= pos0 && (window <= 0 || block_key0 >= last_pos - window + 1);
+          block_key0 + kAttnKeys - 1 <= pos0 && block_key0 >= first_visible_key(last_pos, window, key_chunk);
       uint32_t sv[kAttnGroupKeys];
       tmem_load_64(s_addr, sv);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -481,7 +481,7 @@ static int launch_attention_tc(const CUtensorMap& map_q, const CUtensorMap& map_
                                const CUtensorMap& map_out, void* out,
                                int out_row_stride, const int* q_tiles, int num_tiles, const int* positions,
                                const int* token_seq, const int* seq_seat, const int* block_table, int table_width,
-                               int num_heads, int num_kv_heads, int page_shift, int num_pages, int window,
+                               int num_heads, int num_kv_heads, int page_shift, int num_pages, int window, int key_chunk,
                                float scale_log2, int* error, cudaStream_t stream) {
   const size_t shared = sizeof(AttnShared<D>) + 1024;
   static bool configured = false;
@@ -494,7 +494,7 @@ static int launch_attention_tc(const CUtensorMap& map_q, const CUtensorMap& map_
   const cudaError_t err = launch_dependent_family(
       32, attention_prefill_tcgen05_kernel<D>, dim3(num_heads, num_tiles), dim3(kAttnThreads), shared, stream, map_q,
       map_k, map_v, map_out, (__nv_bfloat16*)out, out_row_stride, q_tiles, positions, token_seq, seq_seat, block_table,
-      table_width, num_heads / num_kv_heads, num_kv_heads, page_shift, num_pages, window, scale_log2, error);
+      table_width, num_heads / num_kv_heads, num_kv_heads, page_shift, num_pages, window, key_chunk, scale_log2, error);
   return err == cudaSuccess ? 0 : (int)err;
 }
 
@@ -511,7 +511,7 @@ extern "C" int distie_attention_prefill_tcgen05(const void* q, int q_row_stride,
                                                 const int* token_seq, const int* seq_seat, const int* block_table,
                                                 int table_width, const void* k_cache, const void* v_cache, int tokens,
                                                 int num_heads, int num_kv_heads, int head_dim, int page_size,
-                                                int num_pages, int window, float scale, int* error,
+                                                int num_pages, int window, int key_chunk, float scale, int* error,
                                                 cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (tokens < 1 || num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || table_width < 1 ||
@@ -535,8 +535,8 @@ extern "C" int distie_attention_prefill_tcgen05(const void* q, int q_row_stride,
   if (head_dim == 64)
     return launch_attention_tc<64>(map_q, map_k, map_v, map_out, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,
                                    seq_seat, block_table, table_width, num_heads, num_kv_heads, page_shift, num_pages,
-                                   window, scale_log2, error, stream);
+                                   window, key_chunk, scale_log2, error, stream);
   return launch_attention_tc<128>(map_q, map_k, map_v, map_out, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,
                                   seq_seat, block_table, table_width, num_heads, num_kv_heads, page_shift, num_pages,
-                                  window, scale_log2, error, stream);
+                                  window, key_chunk, scale_log2, error, stream);
 }

@@ -15,8 +15,11 @@ from .runner import ModelRunner
 
 
 class DecodeBurst:
-    def __init__(self, runner: ModelRunner) -> None:
+    def __init__(self, runner: ModelRunner, state_may_repeat: bool = False) -> None:
+        """``state_may_repeat``: the caller times a model with per-request state and does not mind that the first
+        step of a burst moves that state on twice (the tokens are then not the model's; the time is)."""
         self.runner = runner
+        self.state_may_repeat = bool(state_may_repeat)
         self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}  # bucket size -> (graph, advance)
 
     @torch.inference_mode()
@@ -32,7 +35,7 @@ class DecodeBurst:
             raise ValueError("a burst decodes greedily, one token per request and step")
         if not runner.use_graphs:
             raise RuntimeError("a burst replays captured decode steps: the runner has its graphs switched off")
-        if runner.cache.states:
+        if runner.cache.states and not self.state_may_repeat:
             raise RuntimeError("a burst runs its first step twice, which per-request state does not survive")
         rows = [(item.token_ids[0], item.past_len, item.seq.seat, 0.0, 0.0) for item in items]
         # Stage the rows and make sure the bucket's step is captured (this runs the first step once more than

@@ -421,8 +421,8 @@ class DeviceKernels(KernelSet):
             self._ran("attention_decode_mma" if tensor_cores else "attention_decode", 1 if in_kernel_merge else 2)
         rest = step.num_tokens - n_dec
         tiled = (rest > 0 and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and step.num_q_tiles
-                 and n_dec == step.num_decode_tokens and same and not chunk)
-        if tiled and self._attention_tcgen05(qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale):
+                 and n_dec == step.num_decode_tokens and same)
+        if tiled and self._attention_tcgen05(qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, chunk, scale):
             pass
         elif tiled:
             check(
@@ -430,7 +430,7 @@ class DeviceKernels(KernelSet):
                     qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), step.q_tiles.data_ptr(),
                     step.num_q_tiles, step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
                     kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), num_heads,
-                    num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, float(scale),
+                    num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, chunk, float(scale),
                     self.error_flag.data_ptr(), self._stream(),
                 ),
                 "attention_prefill",
@@ -450,13 +450,13 @@ class DeviceKernels(KernelSet):
             )
             self._ran("attention_generic")
 
-    def _attention_tcgen05(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale) -> bool:
+    def _attention_tcgen05(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, chunk, scale) -> bool:
         """Prompt portions on the tcgen05 kernel; False when it refuses the page size or an alignment."""
         code = function("distie_attention_prefill_tcgen05")(
             qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), step.q_tiles.data_ptr(), step.num_q_tiles,
             step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
             kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), qkv.shape[0],
-            num_heads, num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, float(scale),
+            num_heads, num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, chunk, float(scale),
             self.error_flag.data_ptr(), self._stream(),
         )
         if code == -2:

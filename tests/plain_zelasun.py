@@ -49,26 +49,64 @@ def short_conv(x, taps_weight, bias=None):
     return out
 
 
-def chunked_attention(h, w, p, prm):
-    """Softmax attention without rotation in which position i sees j <= i of its own chunk of
-    ``mask.size`` positions (chunks counted from position 0), a sigmoid gate per head on the output."""
-    heads, kv_heads, dim, vdim = prm["heads"], prm["kv_heads"], prm["dim"], prm["vdim"]
-    size, scale = prm["mask"]["size"], prm["scale"]
-    tokens = h.shape[0]
-    q = (h @ w[p + "q"].T).reshape(tokens, heads, dim)
-    k = (h @ w[p + "k"].T).reshape(tokens, kv_heads, dim)
-    v = (h @ w[p + "v"].T).reshape(tokens, kv_heads, vdim)
-    gate = torch.sigmoid(h @ w[p + "g"].T)  # [T, heads]
-    rep = heads // kv_heads
-    out = torch.zeros(tokens, heads, vdim, dtype=h.dtype)
+def chunked_softmax(q, k, v, scale, size):
+    """``q [T, heads, dim]``, ``k [T, kv_heads, dim]``, ``v [T, kv_heads, vdim]`` -> ``[T, heads, vdim]``:
+    position i sees j <= i of its own chunk of ``size`` positions (chunks counted from position 0)."""
+    tokens, heads, _ = q.shape
+    rep = heads // k.shape[1]
+    out = torch.zeros(tokens, heads, v.shape[2], dtype=q.dtype)
     for i in range(tokens):
         first = (i // size) * size
         for head in range(heads):
             kv = head // rep
             scores = (k[first : i + 1, kv] @ q[i, head]) * scale
             weights = torch.softmax(scores, 0)
-            out[i, head] = (weights[:, None] * v[first : i + 1, kv]).sum(0) * gate[i, head]
+            out[i, head] = (weights[:, None] * v[first : i + 1, kv]).sum(0)
+    return out
+
+
+def chunked_attention(h, w, p, prm):
+    """Softmax attention without rotation over the token's own chunk, a sigmoid gate per head on the output."""
+    heads, kv_heads, dim, vdim = prm["heads"], prm["kv_heads"], prm["dim"], prm["vdim"]
+    tokens = h.shape[0]
+    q = (h @ w[p + "q"].T).reshape(tokens, heads, dim)
+    k = (h @ w[p + "k"].T).reshape(tokens, kv_heads, dim)
+    v = (h @ w[p + "v"].T).reshape(tokens, kv_heads, vdim)
+    gate = torch.sigmoid(h @ w[p + "g"].T)  # [T, heads]
+    out = chunked_softmax(q, k, v, prm["scale"], prm["mask"]["size"]) * gate[:, :, None]
     return out.reshape(tokens, heads * vdim) @ w[p + "o"].T
+
+
+def delta_rule_scan(q, k, v, beta, decay):
+    """``q, k [T, kv_heads, dim]`` (already unit vectors), ``v [T, heads, vdim]``, ``beta, decay [T, heads]``:
+    per head ``S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``, S starting at zero."""
+    tokens, heads, vdim = v.shape
+    dim, rep = q.shape[2], heads // q.shape[1]
+    out = torch.zeros(tokens, heads, vdim, dtype=v.dtype)
+    for head in range(heads):
+        state = torch.zeros(dim, vdim, dtype=v.dtype)
+        kv = head // rep
+        for t in range(tokens):
+            state = decay[t, head] * state
+            write = beta[t, head] * (v[t, head] - state.T @ k[t, kv])
+            state = state + torch.outer(k[t, kv], write)
+            out[t, head] = state.T @ q[t, kv]
+    return out
+
+
+def ssd_scan(x, b, c, dt, rate, skip):
+    """``x [T, heads, vdim]``, ``b, c [T, groups, n]``, ``dt [T, heads]``, ``rate, skip [heads]``:
+    ``S <- exp(-rate dt) S + dt b x^T; y = S^T c + skip x``, S ``[n, vdim]`` starting at zero."""
+    tokens, heads, vdim = x.shape
+    n, rep = b.shape[2], heads // b.shape[1]
+    y = torch.zeros(tokens, heads, vdim, dtype=x.dtype)
+    for head in range(heads):
+        state = torch.zeros(n, vdim, dtype=x.dtype)
+        grp = head // rep
+        for t in range(tokens):
+            state = torch.exp(-rate[head] * dt[t, head]) * state + dt[t, head] * torch.outer(b[t, grp], x[t, head])
+            y[t, head] = state.T @ c[t, grp] + skip[head] * x[t, head]
+    return y
 
 
 def gated_delta_rule(h, w, p, prm, eps):
@@ -83,16 +121,7 @@ def gated_delta_rule(h, w, p, prm, eps):
     beta = torch.sigmoid(h @ w[p + "b"].T)  # [T, heads]
     decay = torch.exp(-torch.exp(w[p + "A_log"]) * softplus(h @ w[p + "a"].T + w[p + "dt_bias"]))  # [T, heads]
     gate = silu(h @ w[p + "g"].T).reshape(tokens, heads, vdim)
-    rep = heads // kv_heads
-    out = torch.zeros(tokens, heads, vdim, dtype=h.dtype)
-    for head in range(heads):
-        state = torch.zeros(dim, vdim, dtype=h.dtype)
-        kv = head // rep
-        for t in range(tokens):
-            state = decay[t, head] * state
-            write = beta[t, head] * (v[t, head] - state.T @ k[t, kv])
-            state = state + torch.outer(k[t, kv], write)
-            out[t, head] = state.T @ q[t, kv]
+    out = delta_rule_scan(q, k, v, beta, decay)
     out = rms_unit(out, eps) * w[p + "norm"] * gate
     return out.reshape(tokens, heads * vdim) @ w[p + "o"].T
 
@@ -116,15 +145,7 @@ def mamba2(h, w, p, prm, eps):
     b = xbc[:, inner : inner + groups * n].reshape(tokens, groups, n)
     c = xbc[:, inner + groups * n :].reshape(tokens, groups, n)
     dt = softplus(dt + w[p + "dt_bias"])  # [T, heads]
-    rate = torch.exp(w[p + "A_log"])
-    rep = heads // groups
-    y = torch.zeros(tokens, heads, vdim, dtype=h.dtype)
-    for head in range(heads):
-        state = torch.zeros(n, vdim, dtype=h.dtype)
-        grp = head // rep
-        for t in range(tokens):
-            state = torch.exp(-rate[head] * dt[t, head]) * state + dt[t, head] * torch.outer(b[t, grp], x[t, head])
-            y[t, head] = state.T @ c[t, grp] + w[p + "D"][head] * x[t, head]
+    y = ssd_scan(x, b, c, dt, torch.exp(w[p + "A_log"]), w[p + "D"])
     y = y.reshape(tokens, inner) * silu(z)
     y = rms_unit(y.reshape(tokens, parts, inner // parts), eps).reshape(tokens, inner) * w[p + "norm"]
     return y @ w[p + "o"].T
