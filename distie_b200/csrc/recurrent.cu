@@ -7,9 +7,11 @@
 // float32 here: inputs are float32 matrices with a row stride (views into a projection's
 // output), state is float32, and only what feeds the next product is stored as T.
 // A step's tokens are ordered by request: `token_seq[t]` (the batch row of token t) never
-// decreases, so the tokens of row b are a range that a binary search finds; `seq_seat[b]`
-// is the request's slot in every state tensor.  Nothing here reads host-side batch data,
-// so captured decode steps replay these kernels for whatever seats they are given.
+// decreases, so the tokens of row b are the range `seq_bounds[b] .. seq_bounds[b + 1] - 1`
+// (made once per step on the device, with `token_first[t]`, the first token of t's request in
+// this step); `seq_seat[b]` is the request's slot in every state tensor.  Nothing here reads
+// host-side batch data, so captured decode steps replay these kernels for whatever seats they
+// are given.
 #include "common.cuh"
 
 namespace distie {
@@ -17,16 +19,6 @@ namespace distie {
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return log1pf(expf(-fabsf(z))) + fmaxf(z, 0.f); }
-
-// First index t in [0, n) with token_seq[t] >= row (n if none).
-__device__ __forceinline__ int first_token_of(const int* __restrict__ token_seq, int n, int row) {
-  int lo = 0, hi = n;
-  while (lo < hi) {
-    const int mid = (lo + hi) >> 1;
-    if (token_seq[mid] < row) lo = mid + 1; else hi = mid;
-  }
-  return lo;
-}
 
 // ---------------------------------------------------------------------------
 // residual += sum_j scale_j * term_j (float32, written back), then
@@ -73,6 +65,61 @@ __global__ void add_layernorm_kernel(SumTerms terms, float* __restrict__ residua
     dst[i] = from_float<T>((row_cache[i] - mean) * inv * weight[i] + bias[i]);
 }
 
+// The same with four columns per thread and the row in registers: hidden a multiple of 4, at most
+// 4 * kNormPieces * blockDim.x, every pointer 16-byte aligned.
+constexpr int kNormPieces = 8;
+template <typename T>
+__global__ void __launch_bounds__(512) add_layernorm_vec_kernel(SumTerms terms, float* __restrict__ residual,
+                                                                const float* __restrict__ weight,
+                                                                const float* __restrict__ bias, T* __restrict__ out,
+                                                                const int* __restrict__ rows_index, int hidden, float eps) {
+  __shared__ float scratch[32];
+  const int out_row = blockIdx.x;
+  const int row = rows_index ? rows_index[out_row] : out_row;
+  float* res = residual + (size_t)row * hidden;
+  const bool write_back = terms.count > 0 && rows_index == nullptr;
+  float4 v[kNormPieces];
+  float sum = 0.f;
+#pragma unroll
+  for (int p = 0; p < kNormPieces; ++p) {
+    const int i = (p * blockDim.x + threadIdx.x) * 4;
+    v[p] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < hidden) {
+      float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int j = 0; j < terms.count; ++j) {
+        const float4 d = *reinterpret_cast<const float4*>(terms.ptr[j] + (size_t)row * hidden + i);
+        const float sc = terms.scale[j];
+        add.x += sc * d.x; add.y += sc * d.y; add.z += sc * d.z; add.w += sc * d.w;
+      }
+      const float4 r = *reinterpret_cast<const float4*>(res + i);
+      v[p] = make_float4(r.x + add.x, r.y + add.y, r.z + add.z, r.w + add.w);
+      if (write_back) *reinterpret_cast<float4*>(res + i) = v[p];
+      sum += (v[p].x + v[p].y) + (v[p].z + v[p].w);
+    }
+  }
+  const float mean = block_sum(sum, scratch) / (float)hidden;
+  float sq = 0.f;
+#pragma unroll
+  for (int p = 0; p < kNormPieces; ++p) {
+    const int i = (p * blockDim.x + threadIdx.x) * 4;
+    if (i < hidden) {
+      const float a = v[p].x - mean, b = v[p].y - mean, c = v[p].z - mean, d = v[p].w - mean;
+      sq += (a * a + b * b) + (c * c + d * d);
+    }
+  }
+  const float inv = 1.f / sqrtf(block_sum(sq, scratch) / (float)hidden + eps);
+  T* dst = out + (size_t)out_row * hidden;
+#pragma unroll
+  for (int p = 0; p < kNormPieces; ++p) {
+    const int i = (p * blockDim.x + threadIdx.x) * 4;
+    if (i < hidden) {
+      const float4 w = *reinterpret_cast<const float4*>(weight + i), b = *reinterpret_cast<const float4*>(bias + i);
+      store4(dst + i, make_float4((v[p].x - mean) * inv * w.x + b.x, (v[p].y - mean) * inv * w.y + b.y,
+                                  (v[p].z - mean) * inv * w.z + b.z, (v[p].w - mean) * inv * w.w + b.w));
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Keys and values of the new tokens into their pages, unrotated; a value may have another size
 // than a key.  One block per token.
@@ -116,56 +163,101 @@ __global__ void head_gate_kernel(T* __restrict__ x, const float* __restrict__ lo
   }
 }
 
+// Four elements a thread: dim a multiple of 4, x aligned to four elements.
+template <typename T>
+__global__ void head_gate_vec_kernel(T* __restrict__ x, const float* __restrict__ logits, int logit_stride, int num_heads,
+                                     int dim, size_t quads) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t e = i * 4;
+    const size_t t = e / ((size_t)num_heads * dim);
+    const int h = (int)((e / dim) % num_heads);
+    const float s = sigmoid_f(logits[t * logit_stride + h]);
+    float4 v = load4(x + e);
+    v.x *= s; v.y *= s; v.z *= s; v.w *= s;
+    store4(x + e, v);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Short causal convolution over time, per channel and per request.
 //   y[t, c] = act(bias[c] + sum_j w[c, taps-1-j] * x_in(t - j)),  j = 0 .. taps-1
 // where x_in reaches back into the request's state (its last taps-1 inputs, oldest first) for
-// tokens before this step's portion.  A second kernel then moves the state on.
+// tokens before this step's portion.  A second kernel then moves the state on; in a step in which
+// every request brings one token (`single` set) the thread that read a channel's state is the only
+// one that does, and moves it on itself.
 // ---------------------------------------------------------------------------
 constexpr int kMaxTaps = 16;
 
 __global__ void short_conv_kernel(const float* __restrict__ x, int x_stride, const float* __restrict__ weight,
-                                  const float* __restrict__ bias, const float* __restrict__ state,
-                                  const int* __restrict__ token_seq, const int* __restrict__ seq_seat, int tokens,
-                                  int channels, int taps, int silu, float* __restrict__ out) {
-  __shared__ int sh_first, sh_seat;
+                                  const float* __restrict__ bias, float* __restrict__ state,
+                                  const int* __restrict__ token_seq, const int* __restrict__ token_first,
+                                  const int* __restrict__ seq_seat, int channels, int taps, int silu, int single,
+                                  float* __restrict__ out) {
   const int t = blockIdx.y;
-  if (threadIdx.x == 0) {
-    const int row = token_seq[t];
-    sh_first = first_token_of(token_seq, tokens, row);
-    sh_seat = seq_seat[row];
-  }
-  __syncthreads();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= channels) return;
-  const int first = sh_first;
-  const float* held = state ? state + (size_t)sh_seat * (taps - 1) * channels : nullptr;
+  const int first = single ? t : token_first[t];
+  float* held = state ? state + (size_t)seq_seat[token_seq[t]] * (taps - 1) * channels : nullptr;
   float acc = bias ? bias[c] : 0.f;
+  float carry = 0.f;  // single: what the slot of the input j places back held before this step (j >= 1)
   for (int j = 0; j < taps; ++j) {
     const int at = t - j;
     float v;
     if (at >= first) v = x[(size_t)at * x_stride + c];
+    else if (single) v = carry;
     else v = held ? held[(size_t)(at - first + taps - 1) * channels + c] : 0.f;
     acc += weight[(size_t)c * taps + (taps - 1 - j)] * v;
+    if (single && held && j < taps - 1) {
+      // the input j places back moves to slot taps-2-j (the current one to the newest slot); what that slot held
+      // is the input j+1 places back, used by the next round
+      float* slot = held + (size_t)(taps - 2 - j) * channels + c;
+      carry = *slot;
+      *slot = v;
+    }
   }
   out[(size_t)t * channels + c] = silu ? silu_f(acc) : acc;
 }
 
-__global__ void short_conv_state_kernel(const float* __restrict__ x, int x_stride, float* __restrict__ state,
-                                        const int* __restrict__ token_seq, const int* __restrict__ seq_seat,
-                                        int tokens, int channels, int taps) {
-  __shared__ int sh_first, sh_end, sh_seat;
-  const int row = blockIdx.y;
-  if (threadIdx.x == 0) {
-    sh_first = first_token_of(token_seq, tokens, row);
-    sh_end = first_token_of(token_seq, tokens, row + 1);
-    sh_seat = seq_seat[row];
+// Four channels a thread for steps that bring portions of prompts: channels and x_stride multiples of 4, x, state
+// and out aligned to 16 bytes.  TAPS > 0: the number of taps at compile time.
+template <int TAPS>
+__global__ void short_conv_vec_kernel(const float* __restrict__ x, int x_stride, const float* __restrict__ weight,
+                                      const float* __restrict__ bias, const float* __restrict__ state,
+                                      const int* __restrict__ token_seq, const int* __restrict__ token_first,
+                                      const int* __restrict__ seq_seat, int channels, int taps_runtime, int silu,
+                                      float* __restrict__ out) {
+  const int taps = TAPS > 0 ? TAPS : taps_runtime;
+  const int t = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (c >= channels) return;
+  const int first = token_first[t];
+  const float* held = state ? state + (size_t)seq_seat[token_seq[t]] * (taps - 1) * channels : nullptr;
+  float4 acc = bias ? *reinterpret_cast<const float4*>(bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int j = 0; j < (TAPS > 0 ? TAPS : kMaxTaps); ++j) {
+    if (j >= taps) break;
+    const int at = t - j;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (at >= first) v = *reinterpret_cast<const float4*>(x + (size_t)at * x_stride + c);
+    else if (held) v = *reinterpret_cast<const float4*>(held + (size_t)(at - first + taps - 1) * channels + c);
+    const int tap = taps - 1 - j;
+    acc.x += weight[(size_t)c * taps + tap] * v.x;
+    acc.y += weight[(size_t)(c + 1) * taps + tap] * v.y;
+    acc.z += weight[(size_t)(c + 2) * taps + tap] * v.z;
+    acc.w += weight[(size_t)(c + 3) * taps + tap] * v.w;
   }
-  __syncthreads();
+  if (silu) acc = make_float4(silu_f(acc.x), silu_f(acc.y), silu_f(acc.z), silu_f(acc.w));
+  *reinterpret_cast<float4*>(out + (size_t)t * channels + c) = acc;
+}
+
+__global__ void short_conv_state_kernel(const float* __restrict__ x, int x_stride, float* __restrict__ state,
+                                        const int* __restrict__ seq_bounds, const int* __restrict__ seq_seat,
+                                        int channels, int taps) {
+  const int row = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  const int first = sh_first, n = sh_end - sh_first;
+  const int first = seq_bounds[row], n = seq_bounds[row + 1] - first;
   if (c >= channels || n <= 0) return;
-  float* held = state + (size_t)sh_seat * (taps - 1) * channels;
+  float* held = state + (size_t)seq_seat[row] * (taps - 1) * channels;
   float next[kMaxTaps];
   for (int i = 0; i < taps - 1; ++i) {
     const int rel = n + i - (taps - 1);  // index among this step's tokens of the request, negative: still the old state
@@ -177,52 +269,147 @@ __global__ void short_conv_state_kernel(const float* __restrict__ x, int x_strid
 // ---------------------------------------------------------------------------
 // Linear recurrence with a matrix state per head and request, float32, token by token:
 //   S <- g S;  S <- S + k u^T;  o = S^T q (+ skip * v)
-// The columns of S (one per value element) never meet, so a column belongs to a group of
-// eight lanes that share its key_dim entries (lane l holds i = 4 l + 32 r + c), and a block
-// of 128 threads owns 16 columns of one head of one request.  Tokens come in tiles of 16:
-// the block stages q, k, the 16 columns of v and the per-token scalars in shared memory,
-// then every group walks the tile without meeting the others.
 //   kDelta: q, k unit vectors (q times key_dim^-1/2); g = exp(-exp(rate) softplus(decay + bias));
 //           u = sigmoid(write) (v - S^T k) with the decayed S.
 //   kSsd:   dt = softplus(write + bias); g = exp(-exp(rate) dt); u = dt v; read-out + skip * v.
 // State layout: [seat, head, value_dim, key_dim] (S transposed: a column is contiguous).
+//
+// Two kernels.  The first is parallel over tokens: it makes what a token contributes without the state
+// (per head g and the factor of u; per group k . q; for the delta rule q and k as unit vectors, in place).
+// The second walks the tokens.  The columns of S (one per value element) never meet, so a column belongs
+// to a group of eight lanes that share its key_dim entries (lane l holds i = 4 l + 32 r + c), and a block
+// of 64 threads owns 8 columns of one head of one request.  The read-out is taken from the state before the
+// write, o = g (S^T q) + u (k . q), which is the same number: both sums over the state then run side by side
+// instead of one after the other.  Tokens come in tiles of 16 that cp.async brings into shared memory a tile
+// ahead of the walk.
 // ---------------------------------------------------------------------------
 constexpr int kRuleDelta = 0, kRuleSsd = 1;
-constexpr int kScanThreads = 128, kScanColumns = 16, kScanTile = 16;
+constexpr int kScanThreads = 64, kScanColumns = 8, kScanTile = 16;
 
 struct ScanArgs {
-  const float *q, *k, *v, *decay, *write;
+  float *q, *k;  // the delta rule normalises them in place
+  const float *v, *decay, *write;
   int q_stride, k_stride, v_stride, decay_stride, write_stride;
   const float *rate, *bias, *skip;
   float* state;
   float* out;
   int out_stride;
-  const int *token_seq, *seq_seat;
+  const int *seq_bounds, *seq_seat;
   int tokens, heads, groups, key_dim, value_dim;
+  float* scalars;  // [tokens, heads, 2]: g and the factor of u
+  float* kq;       // [tokens, groups]: k . q
 };
 
-template <int PER, int RULE>
+template <int RULE>
+__global__ void __launch_bounds__(128) recurrence_prepare_kernel(ScanArgs a) {
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int h = threadIdx.x; h < a.heads; h += blockDim.x) {
+    const float rate = expf(a.rate[h]), bias = a.bias ? a.bias[h] : 0.f;
+    const float w = a.write[(size_t)t * a.write_stride + h];
+    float g, factor;
+    if (RULE == kRuleDelta) {
+      g = expf(-rate * softplus_f(a.decay[(size_t)t * a.decay_stride + h] + bias));
+      factor = sigmoid_f(w);
+    } else {
+      factor = softplus_f(w + bias);
+      g = expf(-rate * factor);
+    }
+    a.scalars[((size_t)t * a.heads + h) * 2] = g;
+    a.scalars[((size_t)t * a.heads + h) * 2 + 1] = factor;
+  }
+  for (int grp = warp; grp < a.groups; grp += 4) {
+    float* q = a.q + (size_t)t * a.q_stride + (size_t)grp * a.key_dim;
+    float* k = a.k + (size_t)t * a.k_stride + (size_t)grp * a.key_dim;
+    float qq = 0.f, kk = 0.f, kq = 0.f;
+    for (int i = lane; i < a.key_dim; i += 32) {
+      const float x = q[i], y = k[i];
+      qq += x * x; kk += y * y; kq += x * y;
+    }
+    kq = warp_sum(kq);
+    if (RULE == kRuleDelta) {
+      qq = warp_sum(qq);
+      kk = warp_sum(kk);
+      const float qs = rsqrtf((float)a.key_dim) / sqrtf(qq + 1e-6f), ks = 1.f / sqrtf(kk + 1e-6f);
+      for (int i = lane; i < a.key_dim; i += 32) { q[i] *= qs; k[i] *= ks; }
+      kq *= qs * ks;
+    }
+    if (lane == 0) a.kq[(size_t)t * a.groups + grp] = kq;
+  }
+}
+
+__device__ __forceinline__ void cp_async_f4(float* dst, const float* src, bool live) {
+  const int bytes = live ? 16 : 0;  // zero-fills when not live
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_f1(float* dst, const float* src, bool live) {
+  const int bytes = live ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One stage of the ring: a tile of q, k (rows of KD floats, zero beyond key_dim), the block's columns of v, and
+// per token g, the factor of u and k . q.
+template <int KD>
+struct ScanStage {
+  float q[kScanTile][KD];
+  float k[kScanTile][KD];
+  float v[kScanTile][kScanColumns];
+  float g[kScanTile], factor[kScanTile], kq[kScanTile];
+};
+
+template <int PER, int RULE, bool VEC>
 __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArgs a) {
   constexpr int KD = 8 * PER;
-  __shared__ __align__(16) float sq[kScanTile][KD];
-  __shared__ __align__(16) float sk[kScanTile][KD];
-  __shared__ float sv[kScanTile][kScanColumns];
-  __shared__ float sg[kScanTile], su[kScanTile];
-  __shared__ int sh_first, sh_end, sh_seat;
+  extern __shared__ __align__(16) unsigned char scan_smem[];
+  ScanStage<KD>* stages = reinterpret_cast<ScanStage<KD>*>(scan_smem);  // two
   const int row = blockIdx.x, head = blockIdx.y;
   const int tid = threadIdx.x, lane8 = tid & 7, col_local = tid >> 3;
   const int j = blockIdx.z * kScanColumns + col_local;
   const bool valid = j < a.value_dim;
   const int grp = head / (a.heads / a.groups);
-  if (tid == 0) {
-    sh_first = first_token_of(a.token_seq, a.tokens, row);
-    sh_end = first_token_of(a.token_seq, a.tokens, row + 1);
-    sh_seat = a.seq_seat[row];
-  }
-  __syncthreads();
-  const int first = sh_first, end = sh_end;
+  const int first = a.seq_bounds[row], end = a.seq_bounds[row + 1];
   if (end <= first) return;
-  float* column = a.state + (((size_t)sh_seat * a.heads + head) * a.value_dim + (valid ? j : 0)) * a.key_dim;
+
+  auto stage_tile = [&](int tile, ScanStage<KD>& st) {
+    const int count = min(kScanTile, end - tile);
+    if (VEC) {
+      for (int idx = tid; idx < count * (KD / 4); idx += kScanThreads) {  // rows past the tile's tokens are never read
+        const int tok = idx / (KD / 4), i = (idx % (KD / 4)) * 4;
+        const bool live = i < a.key_dim;  // columns past key_dim are: zeros, so that they add nothing
+        const size_t t = tile + (live ? tok : 0);
+        const int at = live ? i : 0;
+        cp_async_f4(&st.q[tok][i], a.q + t * a.q_stride + grp * a.key_dim + at, live);
+        cp_async_f4(&st.k[tok][i], a.k + t * a.k_stride + grp * a.key_dim + at, live);
+      }
+    } else {
+      for (int idx = tid; idx < count * KD; idx += kScanThreads) {
+        const int tok = idx / KD, i = idx % KD;
+        const bool live = i < a.key_dim;
+        const size_t t = tile + (live ? tok : 0);
+        const int at = live ? i : 0;
+        cp_async_f1(&st.q[tok][i], a.q + t * a.q_stride + grp * a.key_dim + at, live);
+        cp_async_f1(&st.k[tok][i], a.k + t * a.k_stride + grp * a.key_dim + at, live);
+      }
+    }
+    for (int idx = tid; idx < count * kScanColumns; idx += kScanThreads) {
+      const int tok = idx / kScanColumns, c = idx % kScanColumns, cj = blockIdx.z * kScanColumns + c;
+      const bool live = cj < a.value_dim;
+      cp_async_f1(&st.v[tok][c], a.v + (size_t)(tile + (live ? tok : 0)) * a.v_stride + head * a.value_dim + (live ? cj : 0), live);
+    }
+    if (tid < count) {
+      const bool live = true;
+      const size_t t = tile + tid;
+      cp_async_f1(&st.g[tid], a.scalars + (t * a.heads + head) * 2, live);
+      cp_async_f1(&st.factor[tid], a.scalars + (t * a.heads + head) * 2 + 1, live);
+      cp_async_f1(&st.kq[tid], a.kq + t * a.groups + grp, live);
+    }
+    cp_async_commit();
+  };
+
+  stage_tile(first, stages[0]);
+  float* column = a.state + (((size_t)a.seq_seat[row] * a.heads + head) * a.value_dim + (valid ? j : 0)) * a.key_dim;
   float S[PER];
 #pragma unroll
   for (int r = 0; r < PER / 4; ++r)
@@ -231,84 +418,46 @@ __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArg
       const int i = 4 * lane8 + 32 * r + c;
       S[4 * r + c] = (valid && i < a.key_dim) ? column[i] : 0.f;
     }
-  const float rate = expf(a.rate[head]);
-  const float bias = a.bias ? a.bias[head] : 0.f;
   const float skip = (RULE == kRuleSsd && a.skip) ? a.skip[head] : 0.f;
-  const float q_scale = rsqrtf((float)a.key_dim);
 
-  for (int tile = first; tile < end; tile += kScanTile) {
+  int buffer = 0;
+  for (int tile = first; tile < end; tile += kScanTile, buffer ^= 1) {
     const int count = min(kScanTile, end - tile);
-    __syncthreads();  // the tile before is done with the shared arrays
-    for (int idx = tid; idx < kScanTile * KD; idx += kScanThreads) {
-      const int tok = idx / KD, i = idx % KD;
-      const bool live = tok < count && i < a.key_dim;
-      const size_t t = tile + tok;
-      sq[tok][i] = live ? a.q[t * a.q_stride + grp * a.key_dim + i] : 0.f;
-      sk[tok][i] = live ? a.k[t * a.k_stride + grp * a.key_dim + i] : 0.f;
-    }
-    for (int idx = tid; idx < kScanTile * kScanColumns; idx += kScanThreads) {
-      const int tok = idx / kScanColumns, cj = blockIdx.z * kScanColumns + idx % kScanColumns;
-      sv[tok][idx % kScanColumns] =
-          (tok < count && cj < a.value_dim) ? a.v[(size_t)(tile + tok) * a.v_stride + head * a.value_dim + cj] : 0.f;
-    }
-    if (tid < count) {
-      const size_t t = tile + tid;
-      const float w = a.write[t * a.write_stride + head];
-      if (RULE == kRuleDelta) {
-        sg[tid] = expf(-rate * softplus_f(a.decay[t * a.decay_stride + head] + bias));
-        su[tid] = sigmoid_f(w);
-      } else {
-        const float dt = softplus_f(w + bias);
-        sg[tid] = expf(-rate * dt);
-        su[tid] = dt;
-      }
-    }
+    const bool more = tile + kScanTile < end;
+    if (more) stage_tile(tile + kScanTile, stages[buffer ^ 1]);  // its last readers passed the barrier below
+    if (more) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();
-    if (RULE == kRuleDelta) {  // unit vectors: a warp per token
-      const int lane = tid & 31, warp = tid >> 5;
-      for (int tok = warp; tok < count; tok += kScanThreads / 32) {
-        float qq = 0.f, kk = 0.f;
-        for (int i = lane; i < KD; i += 32) { qq += sq[tok][i] * sq[tok][i]; kk += sk[tok][i] * sk[tok][i]; }
-        qq = warp_sum(qq);
-        kk = warp_sum(kk);
-        const float qs = q_scale / sqrtf(qq + 1e-6f), ks = 1.f / sqrtf(kk + 1e-6f);
-        for (int i = lane; i < KD; i += 32) { sq[tok][i] *= qs; sk[tok][i] *= ks; }
-      }
-      __syncthreads();
-    }
+    const ScanStage<KD>& st = stages[buffer];
     for (int tok = 0; tok < count; ++tok) {
       float kk[PER], qq[PER];
 #pragma unroll
       for (int r = 0; r < PER / 4; ++r) {
-        const float4 kv = *reinterpret_cast<const float4*>(&sk[tok][4 * lane8 + 32 * r]);
-        const float4 qv = *reinterpret_cast<const float4*>(&sq[tok][4 * lane8 + 32 * r]);
+        const float4 kv = *reinterpret_cast<const float4*>(&st.k[tok][4 * lane8 + 32 * r]);
+        const float4 qv = *reinterpret_cast<const float4*>(&st.q[tok][4 * lane8 + 32 * r]);
         kk[4 * r] = kv.x; kk[4 * r + 1] = kv.y; kk[4 * r + 2] = kv.z; kk[4 * r + 3] = kv.w;
         qq[4 * r] = qv.x; qq[4 * r + 1] = qv.y; qq[4 * r + 2] = qv.z; qq[4 * r + 3] = qv.w;
       }
-      const float g = sg[tok], vj = sv[tok][col_local];
-      float u;
-      if (RULE == kRuleDelta) {
-        float dot = 0.f;
-#pragma unroll
-        for (int e = 0; e < PER; ++e) dot += S[e] * kk[e];
-        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-        u = su[tok] * (vj - g * dot);
-      } else {
-        u = su[tok] * vj;
-      }
-      float o = 0.f;
+      const float g = st.g[tok], vj = st.v[tok][col_local];
+      // S^T k and S^T q of this column before the write, four partial sums each
+      float dk[4] = {0.f, 0.f, 0.f, 0.f}, dq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int e = 0; e < PER; ++e) {
-        S[e] = g * S[e] + kk[e] * u;
-        o += S[e] * qq[e];
+        if (RULE == kRuleDelta) dk[e & 3] += S[e] * kk[e];
+        dq[e & 3] += S[e] * qq[e];
       }
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      o += __shfl_xor_sync(0xffffffffu, o, 4);
-      if (lane8 == 0 && valid) a.out[(size_t)(tile + tok) * a.out_stride + head * a.value_dim + j] = o + skip * vj;
+      float sum_k = (dk[0] + dk[1]) + (dk[2] + dk[3]), sum_q = (dq[0] + dq[1]) + (dq[2] + dq[3]);
+#pragma unroll
+      for (int offset = 1; offset < 8; offset <<= 1) {
+        if (RULE == kRuleDelta) sum_k += __shfl_xor_sync(0xffffffffu, sum_k, offset);
+        sum_q += __shfl_xor_sync(0xffffffffu, sum_q, offset);
+      }
+      const float u = RULE == kRuleDelta ? st.factor[tok] * (vj - g * sum_k) : st.factor[tok] * vj;
+#pragma unroll
+      for (int e = 0; e < PER; ++e) S[e] = g * S[e] + kk[e] * u;
+      if (lane8 == 0 && valid)
+        a.out[(size_t)(tile + tok) * a.out_stride + head * a.value_dim + j] = g * sum_q + u * st.kq[tok] + skip * vj;
     }
+    __syncthreads();  // everyone is done with this stage before the copies of the tile after next land in it
   }
   if (valid) {
 #pragma unroll
@@ -321,14 +470,31 @@ __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArg
   }
 }
 
+template <int PER, int RULE>
+static cudaError_t launch_scan_sized(const ScanArgs& a, int num_seqs, bool vec, cudaStream_t stream) {
+  const dim3 grid(num_seqs, a.heads, (a.value_dim + kScanColumns - 1) / kScanColumns);
+  const size_t shared = 2 * sizeof(ScanStage<8 * PER>);
+  auto run = [&](auto kernel) {
+    if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    kernel<<<grid, kScanThreads, shared, stream>>>(a);
+  };
+  if (vec) run(linear_recurrence_kernel<PER, RULE, true>);
+  else run(linear_recurrence_kernel<PER, RULE, false>);
+  return cudaGetLastError();
+}
+
 template <int RULE>
 static cudaError_t launch_scan(const ScanArgs& a, int num_seqs, cudaStream_t stream) {
-  const dim3 grid(num_seqs, a.heads, (a.value_dim + kScanColumns - 1) / kScanColumns);
-  if (a.key_dim <= 32) linear_recurrence_kernel<4, RULE><<<grid, kScanThreads, 0, stream>>>(a);
-  else if (a.key_dim <= 64) linear_recurrence_kernel<8, RULE><<<grid, kScanThreads, 0, stream>>>(a);
-  else if (a.key_dim <= 128) linear_recurrence_kernel<16, RULE><<<grid, kScanThreads, 0, stream>>>(a);
-  else linear_recurrence_kernel<32, RULE><<<grid, kScanThreads, 0, stream>>>(a);
-  return cudaGetLastError();
+  recurrence_prepare_kernel<RULE><<<a.tokens, 128, 0, stream>>>(a);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  // 16-byte copies need rows of q and k that start on 16-byte boundaries
+  const bool vec = a.key_dim % 4 == 0 && a.q_stride % 4 == 0 && a.k_stride % 4 == 0 &&
+                   (((uintptr_t)a.q | (uintptr_t)a.k) & 15) == 0;
+  if (a.key_dim <= 32) return launch_scan_sized<4, RULE>(a, num_seqs, vec, stream);
+  if (a.key_dim <= 64) return launch_scan_sized<8, RULE>(a, num_seqs, vec, stream);
+  if (a.key_dim <= 128) return launch_scan_sized<16, RULE>(a, num_seqs, vec, stream);
+  return launch_scan_sized<32, RULE>(a, num_seqs, vec, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -360,6 +526,48 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ x, int x_stride, 
   }
 }
 
+// Four columns at a time and the group in registers: group a multiple of 4 and at most 128 * kGatedPieces,
+// strides multiples of 4, pointers aligned to 16 bytes (out to four elements).
+constexpr int kGatedPieces = 16;
+template <typename T, int PIECES>
+__global__ void gated_rmsnorm_vec_kernel(const float* __restrict__ x, int x_stride, const float* __restrict__ gate,
+                                         int gate_stride, const float* __restrict__ weight, int weight_len,
+                                         T* __restrict__ out, int out_stride, int tokens, int groups, int group, float eps,
+                                         int gate_first) {
+  const int lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= (long long)tokens * groups) return;
+  const int t = (int)(unit / groups), part = (int)(unit % groups);
+  const float* xr = x + (size_t)t * x_stride + (size_t)part * group;
+  const float* gr = gate + (size_t)t * gate_stride + (size_t)part * group;
+  float4 v[PIECES], s[PIECES];
+  float sq = 0.f;
+#pragma unroll
+  for (int p = 0; p < PIECES; ++p) {
+    const int i = (p * 32 + lane) * 4;
+    if (i < group) {
+      v[p] = *reinterpret_cast<const float4*>(xr + i);
+      const float4 g = *reinterpret_cast<const float4*>(gr + i);
+      s[p] = make_float4(silu_f(g.x), silu_f(g.y), silu_f(g.z), silu_f(g.w));
+      if (gate_first) v[p] = make_float4(v[p].x * s[p].x, v[p].y * s[p].y, v[p].z * s[p].z, v[p].w * s[p].w);
+      sq += (v[p].x * v[p].x + v[p].y * v[p].y) + (v[p].z * v[p].z + v[p].w * v[p].w);
+    }
+  }
+  const float inv = 1.f / sqrtf(warp_sum(sq) / (float)group + eps);
+  T* dst = out + (size_t)t * out_stride + (size_t)part * group;
+#pragma unroll
+  for (int p = 0; p < PIECES; ++p) {
+    const int i = (p * 32 + lane) * 4;
+    if (i < group) {
+      const int at = (part * group + i) % weight_len;  // weight_len is a multiple of 4 here
+      const float4 w = *reinterpret_cast<const float4*>(weight + at);
+      float4 o = make_float4(v[p].x * inv * w.x, v[p].y * inv * w.y, v[p].z * inv * w.z, v[p].w * inv * w.w);
+      if (!gate_first) o = make_float4(o.x * s[p].x, o.y * s[p].y, o.z * s[p].z, o.w * s[p].w);
+      store4(dst + i, o);
+    }
+  }
+}
+
 }  // namespace distie
 
 using namespace distie;
@@ -373,6 +581,22 @@ extern "C" int distie_add_layernorm(const float* const* term_ptrs, const float* 
   SumTerms terms;
   terms.count = num_terms;
   for (int j = 0; j < num_terms; ++j) { terms.ptr[j] = term_ptrs[j]; terms.scale[j] = term_scales[j]; }
+  uintptr_t low_bits = (uintptr_t)residual | (uintptr_t)weight | (uintptr_t)bias | (uintptr_t)out;
+  for (int j = 0; j < num_terms; ++j) low_bits |= (uintptr_t)term_ptrs[j];
+  if (hidden % 4 == 0 && hidden <= 4 * kNormPieces * 512 && (low_bits & 15) == 0 &&
+      (dtype == DISTIE_BF16 || dtype == DISTIE_F32)) {
+    int vec_threads = 32;
+    while (vec_threads < 512 && vec_threads * 8 < hidden) vec_threads *= 2;  // about two pieces a thread
+    while (4 * kNormPieces * vec_threads < hidden) vec_threads *= 2;
+    if (dtype == DISTIE_BF16)
+      add_layernorm_vec_kernel<<<rows, vec_threads, 0, stream>>>(terms, residual, weight, bias, (__nv_bfloat16*)out,
+                                                                 rows_index, hidden, eps);
+    else
+      add_layernorm_vec_kernel<<<rows, vec_threads, 0, stream>>>(terms, residual, weight, bias, (float*)out,
+                                                                 rows_index, hidden, eps);
+    DISTIE_LAUNCH_CHECK();
+    return 0;
+  }
   const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
   const size_t shared = (size_t)hidden * sizeof(float);
   if (shared > 200 * 1024) return DISTIE_ERR_UNSUPPORTED;
@@ -421,6 +645,16 @@ extern "C" int distie_head_gate(void* x, const float* logits, int logit_stride, 
   if (num_heads < 1 || dim < 1) return DISTIE_ERR_ARG;
   const size_t total = (size_t)tokens * num_heads * dim;
   const int threads = 256;
+  if (dim % 4 == 0 && ((uintptr_t)x & 15) == 0 && (dtype == DISTIE_BF16 || dtype == DISTIE_F32)) {
+    const size_t quads = total / 4, want_vec = (quads + threads - 1) / threads;
+    const int blocks_vec = (int)(want_vec < 148 * 32 ? want_vec : 148 * 32);
+    if (dtype == DISTIE_BF16)
+      head_gate_vec_kernel<<<blocks_vec, threads, 0, stream>>>((__nv_bfloat16*)x, logits, logit_stride, num_heads, dim, quads);
+    else
+      head_gate_vec_kernel<<<blocks_vec, threads, 0, stream>>>((float*)x, logits, logit_stride, num_heads, dim, quads);
+    DISTIE_LAUNCH_CHECK();
+    return 0;
+  }
   const size_t want = (total + threads - 1) / threads;
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
   if (dtype == DISTIE_BF16)
@@ -433,46 +667,64 @@ extern "C" int distie_head_gate(void* x, const float* logits, int logit_stride, 
   return 0;
 }
 
-// state may be null only when taps == 1.
+// state may be null only when taps == 1.  `single`: every request of the step brings exactly one token (the
+// caller knows from how the step was laid out); the state is then moved on by the convolution kernel itself.
 extern "C" int distie_short_conv(const float* x, int x_stride, const float* weight, const float* bias, float* state,
-                                 const int* token_seq, const int* seq_seat, int tokens, int num_seqs, int channels,
-                                 int taps, int silu, float* out, cudaStream_t stream) {
+                                 const int* token_seq, const int* token_first, const int* seq_bounds,
+                                 const int* seq_seat, int tokens, int num_seqs, int channels, int taps, int silu,
+                                 int single, float* out, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (channels < 1 || taps < 1 || num_seqs < 1) return DISTIE_ERR_ARG;
   if (taps > kMaxTaps) return DISTIE_ERR_UNSUPPORTED;
   if (taps > 1 && state == nullptr) return DISTIE_ERR_ARG;
   const int threads = 128;
-  const dim3 grid((channels + threads - 1) / threads, tokens);
-  short_conv_kernel<<<grid, threads, 0, stream>>>(x, x_stride, weight, bias, state, token_seq, seq_seat, tokens,
-                                                  channels, taps, silu, out);
+  const bool vec = !single && channels % 4 == 0 && x_stride % 4 == 0 &&
+                   (((uintptr_t)x | (uintptr_t)state | (uintptr_t)out | (uintptr_t)bias) & 15) == 0;
+  if (vec) {
+    const dim3 grid((channels / 4 + threads - 1) / threads, tokens);
+    if (taps == 4)
+      short_conv_vec_kernel<4><<<grid, threads, 0, stream>>>(x, x_stride, weight, bias, state, token_seq, token_first,
+                                                             seq_seat, channels, taps, silu, out);
+    else
+      short_conv_vec_kernel<0><<<grid, threads, 0, stream>>>(x, x_stride, weight, bias, state, token_seq, token_first,
+                                                             seq_seat, channels, taps, silu, out);
+  } else {
+    const dim3 grid((channels + threads - 1) / threads, tokens);
+    short_conv_kernel<<<grid, threads, 0, stream>>>(x, x_stride, weight, bias, state, token_seq, token_first, seq_seat,
+                                                    channels, taps, silu, single, out);
+  }
   DISTIE_LAUNCH_CHECK();
-  if (taps > 1) {
+  if (taps > 1 && !single) {
     const dim3 grid_state((channels + threads - 1) / threads, num_seqs);
-    short_conv_state_kernel<<<grid_state, threads, 0, stream>>>(x, x_stride, state, token_seq, seq_seat, tokens,
-                                                                channels, taps);
+    short_conv_state_kernel<<<grid_state, threads, 0, stream>>>(x, x_stride, state, seq_bounds, seq_seat, channels, taps);
     DISTIE_LAUNCH_CHECK();
   }
   return 0;
 }
 
-extern "C" int distie_linear_recurrence(int rule, const float* q, int q_stride, const float* k, int k_stride,
+// q and k are overwritten by their unit vectors under the delta rule.  scratch: tokens * (2 heads + groups) floats.
+extern "C" int distie_linear_recurrence(int rule, float* q, int q_stride, float* k, int k_stride,
                                         const float* v, int v_stride, const float* decay, int decay_stride,
                                         const float* write, int write_stride, const float* rate, const float* bias,
                                         const float* skip, float* state, float* out, int out_stride,
-                                        const int* token_seq, const int* seq_seat, int tokens, int num_seqs, int heads,
-                                        int groups, int key_dim, int value_dim, cudaStream_t stream) {
+                                        float* scratch, const int* seq_bounds, const int* seq_seat, int tokens,
+                                        int num_seqs, int heads, int groups, int key_dim, int value_dim,
+                                        cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (heads < 1 || groups < 1 || heads % groups || key_dim < 1 || value_dim < 1 || num_seqs < 1 || heads > 65535)
     return DISTIE_ERR_ARG;
   if (key_dim > 256 || (value_dim + kScanColumns - 1) / kScanColumns > 65535) return DISTIE_ERR_UNSUPPORTED;
-  if (rate == nullptr || state == nullptr || (rule == kRuleDelta && decay == nullptr)) return DISTIE_ERR_ARG;
+  if (rate == nullptr || state == nullptr || scratch == nullptr || (rule == kRuleDelta && decay == nullptr))
+    return DISTIE_ERR_ARG;
   ScanArgs a;
   a.q = q; a.k = k; a.v = v; a.decay = decay; a.write = write;
   a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride; a.decay_stride = decay_stride;
   a.write_stride = write_stride;
   a.rate = rate; a.bias = bias; a.skip = skip; a.state = state; a.out = out; a.out_stride = out_stride;
-  a.token_seq = token_seq; a.seq_seat = seq_seat;
+  a.seq_bounds = seq_bounds; a.seq_seat = seq_seat;
   a.tokens = tokens; a.heads = heads; a.groups = groups; a.key_dim = key_dim; a.value_dim = value_dim;
+  a.scalars = scratch;
+  a.kq = scratch + (size_t)tokens * heads * 2;
   cudaError_t err;
   if (rule == kRuleDelta) err = launch_scan<kRuleDelta>(a, num_seqs, stream);
   else if (rule == kRuleSsd) err = launch_scan<kRuleSsd>(a, num_seqs, stream);
@@ -488,6 +740,24 @@ extern "C" int distie_gated_rmsnorm(const float* x, int x_stride, const float* g
   const int groups = n / group, warps = 4;
   const long long units = (long long)tokens * groups;
   const unsigned blocks = (unsigned)((units + warps - 1) / warps);
+  const bool vec = group % 4 == 0 && group <= 128 * kGatedPieces && weight_len % 4 == 0 && x_stride % 4 == 0 &&
+                   gate_stride % 4 == 0 && out_stride % 4 == 0 &&
+                   (((uintptr_t)x | (uintptr_t)gate | (uintptr_t)weight | (uintptr_t)out) & 15) == 0 &&
+                   (dtype == DISTIE_BF16 || dtype == DISTIE_F32);
+  if (vec) {
+#define DISTIE_GATED(T, PIECES)                                                                                        \
+  gated_rmsnorm_vec_kernel<T, PIECES><<<blocks, warps * 32, 0, stream>>>(x, x_stride, gate, gate_stride, weight,         \
+                                                                         weight_len, (T*)out, out_stride, tokens, groups, \
+                                                                         group, eps, gate_first)
+    if (dtype == DISTIE_BF16) {
+      if (group <= 256) DISTIE_GATED(__nv_bfloat16, 2); else DISTIE_GATED(__nv_bfloat16, kGatedPieces);
+    } else {
+      if (group <= 256) DISTIE_GATED(float, 2); else DISTIE_GATED(float, kGatedPieces);
+    }
+#undef DISTIE_GATED
+    DISTIE_LAUNCH_CHECK();
+    return 0;
+  }
   if (dtype == DISTIE_BF16)
     gated_rmsnorm_kernel<<<blocks, warps * 32, 0, stream>>>(x, x_stride, gate, gate_stride, weight, weight_len,
                                                             (__nv_bfloat16*)out, out_stride, tokens, groups, group, eps,

@@ -517,19 +517,32 @@ class DeviceKernels(KernelSet):
         )
         self._ran("head_gate")
 
+    def _seq_index(self, step):
+        """(token_first [T], seq_bounds [B + 1]), int32: where each token's request starts among the step's tokens and
+        the range of every batch row; made once per step on the device and kept with it for all layers."""
+        made = step.derived.get("seq_index")
+        if made is None:
+            rows = torch.arange(step.num_seqs + 1, dtype=torch.int32, device=self.device)
+            bounds = torch.searchsorted(step.token_seq, rows).to(torch.int32)
+            made = step.derived["seq_index"] = (bounds[step.token_seq.long()].contiguous(), bounds)
+        return made
+
     def short_conv(self, x, weight, bias, state, step, activation="silu"):
         self._rows32(x, "short_conv")
         channels, taps = weight.shape
         out = torch.empty((step.num_tokens, channels), dtype=torch.float32, device=x.device)
+        single = step.num_decode_tokens == step.num_tokens  # one token per request: the kernel moves the state on itself
+        token_first, seq_bounds = self._seq_index(step)
         check(
             function("distie_short_conv")(
                 x.data_ptr(), x.stride(0), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
-                state.data_ptr() if state is not None else None, step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
-                step.num_tokens, step.num_seqs, channels, taps, int(activation == "silu"), out.data_ptr(), self._stream(),
+                state.data_ptr() if state is not None else None, step.token_seq.data_ptr(), token_first.data_ptr(),
+                seq_bounds.data_ptr(), step.seq_seat.data_ptr(), step.num_tokens, step.num_seqs, channels, taps, int(activation == "silu"), int(single), out.data_ptr(),
+                self._stream(),
             ),
             "short_conv",
         )
-        self._ran("short_conv", 2 if taps > 1 else 1)
+        self._ran("short_conv", 2 if taps > 1 and not single else 1)
         return out
 
     def linear_recurrence(self, rule, q, k, v, decay, write, state, step, heads, groups, key_dim, value_dim,
@@ -537,17 +550,19 @@ class DeviceKernels(KernelSet):
         for name, t in (("q", q), ("k", k), ("v", v), ("decay", decay), ("write", write)):
             self._rows32(t, f"linear_recurrence {name}")
         out = torch.empty((step.num_tokens, heads * value_dim), dtype=torch.float32, device=q.device)
+        scratch = torch.empty(step.num_tokens * (2 * heads + groups), dtype=torch.float32, device=q.device)
         check(
             function("distie_linear_recurrence")(
                 _RULES[rule], q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
                 decay.data_ptr(), decay.stride(0), write.data_ptr(), write.stride(0), decay_rate.data_ptr(),
                 decay_bias.data_ptr() if decay_bias is not None else None, skip.data_ptr() if skip is not None else None,
-                state.data_ptr(), out.data_ptr(), out.stride(0), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
-                step.num_tokens, step.num_seqs, heads, groups, key_dim, value_dim, self._stream(),
+                state.data_ptr(), out.data_ptr(), out.stride(0), scratch.data_ptr(), self._seq_index(step)[1].data_ptr(),
+                step.seq_seat.data_ptr(), step.num_tokens, step.num_seqs, heads, groups, key_dim, value_dim,
+                self._stream(),
             ),
             "linear_recurrence",
         )
-        self._ran("linear_recurrence")
+        self._ran("linear_recurrence", 2)
         return out
 
     def gated_rmsnorm(self, x, gate, weight, eps, group, gate_first, out) -> None:

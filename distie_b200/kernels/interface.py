@@ -228,7 +228,8 @@ class KernelSet(ABC):
         ``skip [heads]`` adds ``skip_h * v`` to the read-out (``decay`` is not read).
 
         ``state`` is ``[seats, heads, value_dim, key_dim]`` float32 (S transposed), read and written through
-        each token's seat.  Returns float32 ``[T, heads * value_dim]``."""
+        each token's seat.  Returns float32 ``[T, heads * value_dim]``.  A set may overwrite ``q`` and ``k``
+        (with their unit vectors): the caller hands over buffers it no longer needs."""
         raise NotImplementedError
 
     def gated_rmsnorm(self, x, gate, weight, eps: float, group: int, gate_first: bool, out) -> None:

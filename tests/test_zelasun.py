@@ -240,9 +240,10 @@ def _close(have, want, tol, what):
     assert err <= tol, f"{what}: {err:.3e} of the largest value"
 
 
-def test_layernorm_adds_a_weighted_sum_and_norms(kit):
+@pytest.mark.parametrize("width", [200, 201, 2304])
+def test_layernorm_adds_a_weighted_sum_and_norms(kit, width):
     g = torch.Generator().manual_seed(0)
-    tokens, width = 9, 200
+    tokens = 9
     residual = torch.randn(tokens, width, generator=g) * 3 + 1.5
     a, b = torch.randn(2, tokens, width, generator=g), torch.randn(tokens, width, generator=g)
     weight, bias = torch.randn(width, generator=g), torch.randn(width, generator=g)
@@ -262,7 +263,7 @@ def test_layernorm_adds_a_weighted_sum_and_norms(kit):
     _close(picked, want[[7, 2]], 1e-5 if kit.dtype == torch.float32 else 2e-2, "picked rows")
 
 
-@pytest.mark.parametrize("taps,channels", [(4, 37), (2, 130), (1, 8), (7, 16)])
+@pytest.mark.parametrize("taps,channels", [(4, 37), (2, 130), (1, 8), (7, 16), (4, 64), (3, 260)])
 def test_short_conv_in_portions_against_the_whole(kit, taps, channels):
     g = torch.Generator().manual_seed(taps)
     lengths = {0: 23, 2: 9}  # seat -> tokens
@@ -277,7 +278,7 @@ def test_short_conv_in_portions_against_the_whole(kit, taps, channels):
         entries = [(s, [0] * n, done[s], ()) for s, n in cut]
         step, layout = step_for(kit, entries)
         rows = torch.cat([x[sl.seat][sl.past_len : sl.past_len + sl.q_len] for sl in layout.seqs])
-        padded = torch.cat([rows, torch.zeros(rows.shape[0], 3)], dim=1).to(dev)  # a view with a row stride
+        padded = torch.cat([rows, torch.zeros(rows.shape[0], 4)], dim=1).to(dev)  # a view with a row stride
         out = kit.short_conv(padded[:, :channels], weight.to(dev), bias.to(dev), state, step, "silu")
         for sl in layout.seqs:
             got[sl.seat].append(out[sl.start : sl.start + sl.q_len].cpu())
@@ -330,7 +331,8 @@ def test_linear_recurrence_in_portions_against_the_whole(kit, rule, heads, group
         _close(torch.cat(got[s]), want[s], 2e-5, f"{rule} seat {s}")
 
 
-@pytest.mark.parametrize("gate_first,group,weight_len", [(False, 8, 8), (True, 24, 48), (True, 48, 48), (False, 33, 33)])
+@pytest.mark.parametrize("gate_first,group,weight_len", [(False, 8, 8), (True, 24, 48), (True, 48, 48), (False, 33, 33),
+                                                         (True, 640, 640), (False, 300, 300), (True, 2052, 2052)])
 def test_gated_rmsnorm(kit, gate_first, group, weight_len):
     g = torch.Generator().manual_seed(group)
     tokens, n = 5, 2 * group * (2 if weight_len == group else 1)
