@@ -20,6 +20,30 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return log1pf(expf(-fabsf(z))) + fmaxf(z, 0.f); }
 
+// A float32 matrix that may still be the slices of a split product: `splits` matrices `split_stride` floats apart
+// whose sum it is (splits == 1: the matrix itself).  Loads add the slices up, in their order.
+struct Sliced {
+  const float* p;
+  int stride;  // of a row
+  int splits;
+  long long split_stride;
+  __device__ __forceinline__ float at(size_t row, int col) const {
+    const float* q = p + row * stride + col;
+    float v = q[0];
+    for (int s = 1; s < splits; ++s) v += q[(size_t)s * split_stride];
+    return v;
+  }
+  __device__ __forceinline__ float4 at4(size_t row, int col) const {
+    const float* q = p + row * stride + col;
+    float4 v = *reinterpret_cast<const float4*>(q);
+    for (int s = 1; s < splits; ++s) {
+      const float4 w = *reinterpret_cast<const float4*>(q + (size_t)s * split_stride);
+      v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+    }
+    return v;
+  }
+};
+
 // ---------------------------------------------------------------------------
 // residual += sum_j scale_j * term_j (float32, written back), then
 //   out = (residual - mean) / sqrt(var + eps) * weight + bias,  var = mean((residual - mean)^2).
@@ -154,24 +178,22 @@ __global__ void kv_write_kernel(const TIn* __restrict__ k, int k_stride, const T
 
 // x[t, h, :] *= sigmoid(logits[t, h]).
 template <typename T>
-__global__ void head_gate_kernel(T* __restrict__ x, const float* __restrict__ logits, int logit_stride, int num_heads,
-                                 int dim, size_t total) {
+__global__ void head_gate_kernel(T* __restrict__ x, Sliced logits, int num_heads, int dim, size_t total) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / ((size_t)num_heads * dim);
     const int h = (int)((i / dim) % num_heads);
-    x[i] = from_float<T>(to_float(x[i]) * sigmoid_f(logits[t * logit_stride + h]));
+    x[i] = from_float<T>(to_float(x[i]) * sigmoid_f(logits.at(t, h)));
   }
 }
 
 // Four elements a thread: dim a multiple of 4, x aligned to four elements.
 template <typename T>
-__global__ void head_gate_vec_kernel(T* __restrict__ x, const float* __restrict__ logits, int logit_stride, int num_heads,
-                                     int dim, size_t quads) {
+__global__ void head_gate_vec_kernel(T* __restrict__ x, Sliced logits, int num_heads, int dim, size_t quads) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (size_t)gridDim.x * blockDim.x) {
     const size_t e = i * 4;
     const size_t t = e / ((size_t)num_heads * dim);
     const int h = (int)((e / dim) % num_heads);
-    const float s = sigmoid_f(logits[t * logit_stride + h]);
+    const float s = sigmoid_f(logits.at(t, h));
     float4 v = load4(x + e);
     v.x *= s; v.y *= s; v.z *= s; v.w *= s;
     store4(x + e, v);
@@ -188,7 +210,7 @@ __global__ void head_gate_vec_kernel(T* __restrict__ x, const float* __restrict_
 // ---------------------------------------------------------------------------
 constexpr int kMaxTaps = 16;
 
-__global__ void short_conv_kernel(const float* __restrict__ x, int x_stride, const float* __restrict__ weight,
+__global__ void short_conv_kernel(Sliced x, const float* __restrict__ weight,
                                   const float* __restrict__ bias, float* __restrict__ state,
                                   const int* __restrict__ token_seq, const int* __restrict__ token_first,
                                   const int* __restrict__ seq_seat, int channels, int taps, int silu, int single,
@@ -203,7 +225,7 @@ __global__ void short_conv_kernel(const float* __restrict__ x, int x_stride, con
   for (int j = 0; j < taps; ++j) {
     const int at = t - j;
     float v;
-    if (at >= first) v = x[(size_t)at * x_stride + c];
+    if (at >= first) v = x.at(at, c);
     else if (single) v = carry;
     else v = held ? held[(size_t)(at - first + taps - 1) * channels + c] : 0.f;
     acc += weight[(size_t)c * taps + (taps - 1 - j)] * v;
@@ -218,10 +240,51 @@ __global__ void short_conv_kernel(const float* __restrict__ x, int x_stride, con
   out[(size_t)t * channels + c] = silu ? silu_f(acc) : acc;
 }
 
+// A step in which every request brings one token: the thread reads its channel's taps-1 held inputs at once,
+// and writes them back one slot down with the current input behind them.
+__global__ void short_conv_single_kernel(Sliced x, const float* __restrict__ weight, const float* __restrict__ bias,
+                                         float* __restrict__ state, const int* __restrict__ token_seq,
+                                         const int* __restrict__ seq_seat, int channels, int taps, int silu,
+                                         float* __restrict__ out) {
+  const int t = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  float* held = state + (size_t)seq_seat[token_seq[t]] * (taps - 1) * channels + c;
+  float old[kMaxTaps - 1];
+#pragma unroll
+  for (int i = 0; i < kMaxTaps - 1; ++i) old[i] = i < taps - 1 ? held[(size_t)i * channels] : 0.f;
+  const float now = x.at(t, c);
+  float acc = (bias ? bias[c] : 0.f) + weight[(size_t)c * taps + taps - 1] * now;
+#pragma unroll
+  for (int i = 0; i < kMaxTaps - 1; ++i)
+    if (i < taps - 1) acc += weight[(size_t)c * taps + i] * old[i];  // slot i holds the input taps-1-i places back
+#pragma unroll
+  for (int i = 0; i < kMaxTaps - 1; ++i)
+    if (i < taps - 1) held[(size_t)i * channels] = i + 1 < taps - 1 ? old[i + 1] : now;
+  out[(size_t)t * channels + c] = silu ? silu_f(acc) : acc;
+}
+
+// Where each request's tokens lie in the step: seq_bounds[b] .. seq_bounds[b + 1] - 1 are the tokens of batch row b
+// and token_first[t] is the first token of t's row.  One block.
+__global__ void seq_index_kernel(const int* __restrict__ token_seq, int tokens, int num_seqs, int* __restrict__ token_first,
+                                 int* __restrict__ seq_bounds) {
+  for (int b = threadIdx.x; b <= num_seqs; b += blockDim.x) seq_bounds[b] = tokens;
+  __syncthreads();
+  for (int t = threadIdx.x; t < tokens; t += blockDim.x) {
+    const int row = token_seq[t];
+    if (row >= 0 && row < num_seqs && (t == 0 || token_seq[t - 1] != row)) seq_bounds[row] = t;
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < tokens; t += blockDim.x) {
+    const int row = token_seq[t];
+    token_first[t] = (row >= 0 && row < num_seqs) ? seq_bounds[row] : t;
+  }
+}
+
 // Four channels a thread for steps that bring portions of prompts: channels and x_stride multiples of 4, x, state
 // and out aligned to 16 bytes.  TAPS > 0: the number of taps at compile time.
 template <int TAPS>
-__global__ void short_conv_vec_kernel(const float* __restrict__ x, int x_stride, const float* __restrict__ weight,
+__global__ void short_conv_vec_kernel(Sliced x, const float* __restrict__ weight,
                                       const float* __restrict__ bias, const float* __restrict__ state,
                                       const int* __restrict__ token_seq, const int* __restrict__ token_first,
                                       const int* __restrict__ seq_seat, int channels, int taps_runtime, int silu,
@@ -238,7 +301,7 @@ __global__ void short_conv_vec_kernel(const float* __restrict__ x, int x_stride,
     if (j >= taps) break;
     const int at = t - j;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (at >= first) v = *reinterpret_cast<const float4*>(x + (size_t)at * x_stride + c);
+    if (at >= first) v = x.at4(at, c);
     else if (held) v = *reinterpret_cast<const float4*>(held + (size_t)(at - first + taps - 1) * channels + c);
     const int tap = taps - 1 - j;
     acc.x += weight[(size_t)c * taps + tap] * v.x;
@@ -250,7 +313,7 @@ __global__ void short_conv_vec_kernel(const float* __restrict__ x, int x_stride,
   *reinterpret_cast<float4*>(out + (size_t)t * channels + c) = acc;
 }
 
-__global__ void short_conv_state_kernel(const float* __restrict__ x, int x_stride, float* __restrict__ state,
+__global__ void short_conv_state_kernel(Sliced x, float* __restrict__ state,
                                         const int* __restrict__ seq_bounds, const int* __restrict__ seq_seat,
                                         int channels, int taps) {
   const int row = blockIdx.y;
@@ -261,7 +324,7 @@ __global__ void short_conv_state_kernel(const float* __restrict__ x, int x_strid
   float next[kMaxTaps];
   for (int i = 0; i < taps - 1; ++i) {
     const int rel = n + i - (taps - 1);  // index among this step's tokens of the request, negative: still the old state
-    next[i] = rel >= 0 ? x[(size_t)(first + rel) * x_stride + c] : held[(size_t)(i + n) * channels + c];
+    next[i] = rel >= 0 ? x.at(first + rel, c) : held[(size_t)(i + n) * channels + c];
   }
   for (int i = 0; i < taps - 1; ++i) held[(size_t)i * channels + c] = next[i];
 }
@@ -290,6 +353,8 @@ struct ScanArgs {
   float *q, *k;  // the delta rule normalises them in place
   const float *v, *decay, *write;
   int q_stride, k_stride, v_stride, decay_stride, write_stride;
+  int splits;              // decay and write may be slices of a split product
+  long long split_stride;
   const float *rate, *bias, *skip;
   float* state;
   float* out;
@@ -305,10 +370,10 @@ __global__ void __launch_bounds__(128) recurrence_prepare_kernel(ScanArgs a) {
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int h = threadIdx.x; h < a.heads; h += blockDim.x) {
     const float rate = expf(a.rate[h]), bias = a.bias ? a.bias[h] : 0.f;
-    const float w = a.write[(size_t)t * a.write_stride + h];
+    const float w = Sliced{a.write, a.write_stride, a.splits, a.split_stride}.at(t, h);
     float g, factor;
     if (RULE == kRuleDelta) {
-      g = expf(-rate * softplus_f(a.decay[(size_t)t * a.decay_stride + h] + bias));
+      g = expf(-rate * softplus_f(Sliced{a.decay, a.decay_stride, a.splits, a.split_stride}.at(t, h) + bias));
       factor = sigmoid_f(w);
     } else {
       factor = softplus_f(w + bias);
@@ -503,61 +568,62 @@ static cudaError_t launch_scan(const ScanArgs& a, int num_seqs, cudaStream_t str
 // weight has `weight_len` elements and repeats along the row.
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void gated_rmsnorm_kernel(const float* __restrict__ x, int x_stride, const float* __restrict__ gate,
-                                     int gate_stride, const float* __restrict__ weight, int weight_len, T* __restrict__ out,
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ x, int x_stride, Sliced gate,
+                                     const float* __restrict__ weight, int weight_len, T* __restrict__ out,
                                      int out_stride, int tokens, int groups, int group, float eps, int gate_first) {
   const int lane = threadIdx.x & 31;
   const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= (long long)tokens * groups) return;
   const int t = (int)(unit / groups), part = (int)(unit % groups);
   const float* xr = x + (size_t)t * x_stride + (size_t)part * group;
-  const float* gr = gate + (size_t)t * gate_stride + (size_t)part * group;
   float sq = 0.f;
   for (int i = lane; i < group; i += 32) {
-    const float v = gate_first ? xr[i] * silu_f(gr[i]) : xr[i];
+    const float v = gate_first ? xr[i] * silu_f(gate.at(t, part * group + i)) : xr[i];
     sq += v * v;
   }
   const float inv = 1.f / sqrtf(warp_sum(sq) / (float)group + eps);
   T* dst = out + (size_t)t * out_stride + (size_t)part * group;
   for (int i = lane; i < group; i += 32) {
-    const float s = silu_f(gr[i]);
+    const float s = silu_f(gate.at(t, part * group + i));
     const float w = weight[(part * group + i) % weight_len];
     dst[i] = from_float<T>(gate_first ? xr[i] * s * inv * w : xr[i] * inv * w * s);
   }
 }
 
-// Four columns at a time and the group in registers: group a multiple of 4 and at most 128 * kGatedPieces,
-// strides multiples of 4, pointers aligned to 16 bytes (out to four elements).
-constexpr int kGatedPieces = 16;
-template <typename T, int PIECES>
-__global__ void gated_rmsnorm_vec_kernel(const float* __restrict__ x, int x_stride, const float* __restrict__ gate,
-                                         int gate_stride, const float* __restrict__ weight, int weight_len,
-                                         T* __restrict__ out, int out_stride, int tokens, int groups, int group, float eps,
-                                         int gate_first) {
-  const int lane = threadIdx.x & 31;
-  const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (unit >= (long long)tokens * groups) return;
+// Four columns at a time and the group in registers: group a multiple of 4 and at most 4 * LANES * PIECES,
+// strides multiples of 4, pointers aligned to 16 bytes (out to four elements).  LANES threads share a
+// (token, group): a warp (LANES = 32, four of them to a block) or a whole block (LANES = blockDim.x = 256).
+template <typename T, int PIECES, int LANES>
+__global__ void __launch_bounds__(LANES == 32 ? 128 : LANES)
+gated_rmsnorm_vec_kernel(const float* __restrict__ x, int x_stride, Sliced gate, const float* __restrict__ weight,
+                         int weight_len, T* __restrict__ out, int out_stride, int tokens, int groups, int group,
+                         float eps, int gate_first) {
+  __shared__ float scratch[32];
+  const int lane = threadIdx.x % LANES;
+  const long long unit = LANES == 32 ? (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5) : blockIdx.x;
+  const bool live = unit < (long long)tokens * groups;  // (a block is either wholly live or a warp per unit)
+  if (LANES == 32 && !live) return;
   const int t = (int)(unit / groups), part = (int)(unit % groups);
   const float* xr = x + (size_t)t * x_stride + (size_t)part * group;
-  const float* gr = gate + (size_t)t * gate_stride + (size_t)part * group;
   float4 v[PIECES], s[PIECES];
   float sq = 0.f;
 #pragma unroll
   for (int p = 0; p < PIECES; ++p) {
-    const int i = (p * 32 + lane) * 4;
+    const int i = (p * LANES + lane) * 4;
     if (i < group) {
       v[p] = *reinterpret_cast<const float4*>(xr + i);
-      const float4 g = *reinterpret_cast<const float4*>(gr + i);
+      const float4 g = gate.at4(t, part * group + i);
       s[p] = make_float4(silu_f(g.x), silu_f(g.y), silu_f(g.z), silu_f(g.w));
       if (gate_first) v[p] = make_float4(v[p].x * s[p].x, v[p].y * s[p].y, v[p].z * s[p].z, v[p].w * s[p].w);
       sq += (v[p].x * v[p].x + v[p].y * v[p].y) + (v[p].z * v[p].z + v[p].w * v[p].w);
     }
   }
-  const float inv = 1.f / sqrtf(warp_sum(sq) / (float)group + eps);
+  const float total = LANES == 32 ? warp_sum(sq) : block_sum(sq, scratch);
+  const float inv = 1.f / sqrtf(total / (float)group + eps);
   T* dst = out + (size_t)t * out_stride + (size_t)part * group;
 #pragma unroll
   for (int p = 0; p < PIECES; ++p) {
-    const int i = (p * 32 + lane) * 4;
+    const int i = (p * LANES + lane) * 4;
     if (i < group) {
       const int at = (part * group + i) % weight_len;  // weight_len is a multiple of 4 here
       const float4 w = *reinterpret_cast<const float4*>(weight + at);
@@ -639,37 +705,47 @@ extern "C" int distie_kv_write(const void* k, int k_stride, const void* v, int v
   return 0;
 }
 
-extern "C" int distie_head_gate(void* x, const float* logits, int logit_stride, int tokens, int num_heads, int dim,
-                                int dtype, cudaStream_t stream) {
+extern "C" int distie_head_gate(void* x, const float* logits_ptr, int logit_stride, int splits, long long split_stride,
+                                int tokens, int num_heads, int dim, int dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (num_heads < 1 || dim < 1) return DISTIE_ERR_ARG;
+  if (num_heads < 1 || dim < 1 || splits < 1) return DISTIE_ERR_ARG;
+  const Sliced logits{logits_ptr, logit_stride, splits, split_stride};
   const size_t total = (size_t)tokens * num_heads * dim;
   const int threads = 256;
   if (dim % 4 == 0 && ((uintptr_t)x & 15) == 0 && (dtype == DISTIE_BF16 || dtype == DISTIE_F32)) {
     const size_t quads = total / 4, want_vec = (quads + threads - 1) / threads;
     const int blocks_vec = (int)(want_vec < 148 * 32 ? want_vec : 148 * 32);
     if (dtype == DISTIE_BF16)
-      head_gate_vec_kernel<<<blocks_vec, threads, 0, stream>>>((__nv_bfloat16*)x, logits, logit_stride, num_heads, dim, quads);
+      head_gate_vec_kernel<<<blocks_vec, threads, 0, stream>>>((__nv_bfloat16*)x, logits, num_heads, dim, quads);
     else
-      head_gate_vec_kernel<<<blocks_vec, threads, 0, stream>>>((float*)x, logits, logit_stride, num_heads, dim, quads);
+      head_gate_vec_kernel<<<blocks_vec, threads, 0, stream>>>((float*)x, logits, num_heads, dim, quads);
     DISTIE_LAUNCH_CHECK();
     return 0;
   }
   const size_t want = (total + threads - 1) / threads;
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
   if (dtype == DISTIE_BF16)
-    head_gate_kernel<<<blocks, threads, 0, stream>>>((__nv_bfloat16*)x, logits, logit_stride, num_heads, dim, total);
+    head_gate_kernel<<<blocks, threads, 0, stream>>>((__nv_bfloat16*)x, logits, num_heads, dim, total);
   else if (dtype == DISTIE_F32)
-    head_gate_kernel<<<blocks, threads, 0, stream>>>((float*)x, logits, logit_stride, num_heads, dim, total);
+    head_gate_kernel<<<blocks, threads, 0, stream>>>((float*)x, logits, num_heads, dim, total);
   else
     return DISTIE_ERR_UNSUPPORTED;
   DISTIE_LAUNCH_CHECK();
   return 0;
 }
 
+extern "C" int distie_seq_index(const int* token_seq, int tokens, int num_seqs, int* token_first, int* seq_bounds,
+                                cudaStream_t stream) {
+  if (tokens <= 0 || num_seqs < 1) return DISTIE_ERR_ARG;
+  seq_index_kernel<<<1, 1024, 0, stream>>>(token_seq, tokens, num_seqs, token_first, seq_bounds);
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
 // state may be null only when taps == 1.  `single`: every request of the step brings exactly one token (the
 // caller knows from how the step was laid out); the state is then moved on by the convolution kernel itself.
-extern "C" int distie_short_conv(const float* x, int x_stride, const float* weight, const float* bias, float* state,
+extern "C" int distie_short_conv(const float* x_ptr, int x_stride, int splits, long long split_stride,
+                                 const float* weight, const float* bias, float* state,
                                  const int* token_seq, const int* token_first, const int* seq_bounds,
                                  const int* seq_seat, int tokens, int num_seqs, int channels, int taps, int silu,
                                  int single, float* out, cudaStream_t stream) {
@@ -677,35 +753,43 @@ extern "C" int distie_short_conv(const float* x, int x_stride, const float* weig
   if (channels < 1 || taps < 1 || num_seqs < 1) return DISTIE_ERR_ARG;
   if (taps > kMaxTaps) return DISTIE_ERR_UNSUPPORTED;
   if (taps > 1 && state == nullptr) return DISTIE_ERR_ARG;
+  if (splits < 1) return DISTIE_ERR_ARG;
+  const Sliced x{x_ptr, x_stride, splits, split_stride};
   const int threads = 128;
-  const bool vec = !single && channels % 4 == 0 && x_stride % 4 == 0 &&
-                   (((uintptr_t)x | (uintptr_t)state | (uintptr_t)out | (uintptr_t)bias) & 15) == 0;
+  const bool vec = !single && channels % 4 == 0 && x_stride % 4 == 0 && split_stride % 4 == 0 &&
+                   (((uintptr_t)x_ptr | (uintptr_t)state | (uintptr_t)out | (uintptr_t)bias) & 15) == 0;
   if (vec) {
     const dim3 grid((channels / 4 + threads - 1) / threads, tokens);
     if (taps == 4)
-      short_conv_vec_kernel<4><<<grid, threads, 0, stream>>>(x, x_stride, weight, bias, state, token_seq, token_first,
+      short_conv_vec_kernel<4><<<grid, threads, 0, stream>>>(x, weight, bias, state, token_seq, token_first,
                                                              seq_seat, channels, taps, silu, out);
     else
-      short_conv_vec_kernel<0><<<grid, threads, 0, stream>>>(x, x_stride, weight, bias, state, token_seq, token_first,
+      short_conv_vec_kernel<0><<<grid, threads, 0, stream>>>(x, weight, bias, state, token_seq, token_first,
                                                              seq_seat, channels, taps, silu, out);
+  } else if (single && taps > 1) {
+    const dim3 grid((channels + threads - 1) / threads, tokens);
+    short_conv_single_kernel<<<grid, threads, 0, stream>>>(x, weight, bias, state, token_seq, seq_seat, channels, taps,
+                                                           silu, out);
   } else {
     const dim3 grid((channels + threads - 1) / threads, tokens);
-    short_conv_kernel<<<grid, threads, 0, stream>>>(x, x_stride, weight, bias, state, token_seq, token_first, seq_seat,
+    short_conv_kernel<<<grid, threads, 0, stream>>>(x, weight, bias, state, token_seq, token_first, seq_seat,
                                                     channels, taps, silu, single, out);
   }
   DISTIE_LAUNCH_CHECK();
   if (taps > 1 && !single) {
     const dim3 grid_state((channels + threads - 1) / threads, num_seqs);
-    short_conv_state_kernel<<<grid_state, threads, 0, stream>>>(x, x_stride, state, seq_bounds, seq_seat, channels, taps);
+    short_conv_state_kernel<<<grid_state, threads, 0, stream>>>(x, state, seq_bounds, seq_seat, channels, taps);
     DISTIE_LAUNCH_CHECK();
   }
   return 0;
 }
 
 // q and k are overwritten by their unit vectors under the delta rule.  scratch: tokens * (2 heads + groups) floats.
+// decay and write may be slices of a split product (`splits` of them, `split_stride` floats apart).
 extern "C" int distie_linear_recurrence(int rule, float* q, int q_stride, float* k, int k_stride,
                                         const float* v, int v_stride, const float* decay, int decay_stride,
-                                        const float* write, int write_stride, const float* rate, const float* bias,
+                                        const float* write, int write_stride, int splits, long long split_stride,
+                                        const float* rate, const float* bias,
                                         const float* skip, float* state, float* out, int out_stride,
                                         float* scratch, const int* seq_bounds, const int* seq_seat, int tokens,
                                         int num_seqs, int heads, int groups, int key_dim, int value_dim,
@@ -720,6 +804,7 @@ extern "C" int distie_linear_recurrence(int rule, float* q, int q_stride, float*
   a.q = q; a.k = k; a.v = v; a.decay = decay; a.write = write;
   a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride; a.decay_stride = decay_stride;
   a.write_stride = write_stride;
+  a.splits = splits < 1 ? 1 : splits; a.split_stride = split_stride;
   a.rate = rate; a.bias = bias; a.skip = skip; a.state = state; a.out = out; a.out_stride = out_stride;
   a.seq_bounds = seq_bounds; a.seq_seat = seq_seat;
   a.tokens = tokens; a.heads = heads; a.groups = groups; a.key_dim = key_dim; a.value_dim = value_dim;
@@ -732,42 +817,41 @@ extern "C" int distie_linear_recurrence(int rule, float* q, int q_stride, float*
   return err == cudaSuccess ? 0 : (int)err;
 }
 
-extern "C" int distie_gated_rmsnorm(const float* x, int x_stride, const float* gate, int gate_stride,
-                                    const float* weight, int weight_len, void* out, int out_stride, int tokens, int n,
-                                    int group, float eps, int gate_first, int dtype, cudaStream_t stream) {
+extern "C" int distie_gated_rmsnorm(const float* x, int x_stride, const float* gate_ptr, int gate_stride, int splits,
+                                    long long split_stride, const float* weight, int weight_len, void* out,
+                                    int out_stride, int tokens, int n, int group, float eps, int gate_first, int dtype,
+                                    cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (n < 1 || group < 1 || n % group || weight_len < 1) return DISTIE_ERR_ARG;
+  if (n < 1 || group < 1 || n % group || weight_len < 1 || splits < 1) return DISTIE_ERR_ARG;
+  if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
+  const Sliced gate{gate_ptr, gate_stride, splits, split_stride};
   const int groups = n / group, warps = 4;
   const long long units = (long long)tokens * groups;
   const unsigned blocks = (unsigned)((units + warps - 1) / warps);
-  const bool vec = group % 4 == 0 && group <= 128 * kGatedPieces && weight_len % 4 == 0 && x_stride % 4 == 0 &&
-                   gate_stride % 4 == 0 && out_stride % 4 == 0 &&
-                   (((uintptr_t)x | (uintptr_t)gate | (uintptr_t)weight | (uintptr_t)out) & 15) == 0 &&
-                   (dtype == DISTIE_BF16 || dtype == DISTIE_F32);
-  if (vec) {
-#define DISTIE_GATED(T, PIECES)                                                                                        \
-  gated_rmsnorm_vec_kernel<T, PIECES><<<blocks, warps * 32, 0, stream>>>(x, x_stride, gate, gate_stride, weight,         \
-                                                                         weight_len, (T*)out, out_stride, tokens, groups, \
-                                                                         group, eps, gate_first)
-    if (dtype == DISTIE_BF16) {
-      if (group <= 256) DISTIE_GATED(__nv_bfloat16, 2); else DISTIE_GATED(__nv_bfloat16, kGatedPieces);
-    } else {
-      if (group <= 256) DISTIE_GATED(float, 2); else DISTIE_GATED(float, kGatedPieces);
-    }
+  const bool vec = group % 4 == 0 && group <= 4 * 256 * 8 && weight_len % 4 == 0 && x_stride % 4 == 0 &&
+                   gate_stride % 4 == 0 && split_stride % 4 == 0 && out_stride % 4 == 0 &&
+                   (((uintptr_t)x | (uintptr_t)gate_ptr | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
+#define DISTIE_GATED(T)                                                                                                  \
+  do {                                                                                                                   \
+    if (!vec)                                                                                                            \
+      gated_rmsnorm_kernel<<<blocks, warps * 32, 0, stream>>>(x, x_stride, gate, weight, weight_len, (T*)out, out_stride, \
+                                                              tokens, groups, group, eps, gate_first);                   \
+    else if (group <= 256)                                                                                               \
+      gated_rmsnorm_vec_kernel<T, 2, 32><<<blocks, warps * 32, 0, stream>>>(x, x_stride, gate, weight, weight_len,        \
+                                                                            (T*)out, out_stride, tokens, groups, group,   \
+                                                                            eps, gate_first);                            \
+    else if (group <= 2048)                                                                                              \
+      gated_rmsnorm_vec_kernel<T, 2, 256><<<(unsigned)units, 256, 0, stream>>>(x, x_stride, gate, weight, weight_len,     \
+                                                                               (T*)out, out_stride, tokens, groups,       \
+                                                                               group, eps, gate_first);                  \
+    else                                                                                                                 \
+      gated_rmsnorm_vec_kernel<T, 8, 256><<<(unsigned)units, 256, 0, stream>>>(x, x_stride, gate, weight, weight_len,     \
+                                                                               (T*)out, out_stride, tokens, groups,       \
+                                                                               group, eps, gate_first);                  \
+  } while (0)
+  if (dtype == DISTIE_BF16) DISTIE_GATED(__nv_bfloat16);
+  else DISTIE_GATED(float);
 #undef DISTIE_GATED
-    DISTIE_LAUNCH_CHECK();
-    return 0;
-  }
-  if (dtype == DISTIE_BF16)
-    gated_rmsnorm_kernel<<<blocks, warps * 32, 0, stream>>>(x, x_stride, gate, gate_stride, weight, weight_len,
-                                                            (__nv_bfloat16*)out, out_stride, tokens, groups, group, eps,
-                                                            gate_first);
-  else if (dtype == DISTIE_F32)
-    gated_rmsnorm_kernel<<<blocks, warps * 32, 0, stream>>>(x, x_stride, gate, gate_stride, weight, weight_len,
-                                                            (float*)out, out_stride, tokens, groups, group, eps,
-                                                            gate_first);
-  else
-    return DISTIE_ERR_UNSUPPORTED;
   DISTIE_LAUNCH_CHECK();
   return 0;
 }

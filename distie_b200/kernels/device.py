@@ -490,6 +490,14 @@ class DeviceKernels(KernelSet):
             raise KernelError(f"{what}: a float32 matrix with unit column stride is expected")
         return x
 
+    @classmethod
+    def _sliced(cls, x: torch.Tensor, what: str) -> tuple[int, int, int, int]:
+        """(pointer, row stride, slices, slice stride) of a float32 matrix or of the slices ``[S, T, n]`` it is the sum of."""
+        cls._rows32(x, what)
+        if x.dim() == 3:
+            return x.data_ptr(), x.stride(1), x.shape[0], x.stride(0)
+        return x.data_ptr(), x.stride(0), 1, 0
+
     def kv_write(self, k, v, step, kv) -> None:
         if k.dtype != v.dtype or k.dtype not in _CODE or k.stride(1) != 1 or v.stride(1) != 1:
             raise KernelError("kv_write: keys and values of one float type with unit column stride are expected")
@@ -505,12 +513,11 @@ class DeviceKernels(KernelSet):
         self._ran("kv_write")
 
     def head_gate(self, x, logits, num_heads) -> None:
-        self._rows32(logits, "head_gate")
         if not x.is_contiguous():
             raise KernelError("head_gate: a contiguous activation is expected")
         check(
             function("distie_head_gate")(
-                x.data_ptr(), logits.data_ptr(), logits.stride(0), x.shape[0], num_heads, x.shape[1] // num_heads,
+                x.data_ptr(), *self._sliced(logits, "head_gate"), x.shape[0], num_heads, x.shape[1] // num_heads,
                 _CODE[x.dtype], self._stream(),
             ),
             "head_gate",
@@ -522,20 +529,26 @@ class DeviceKernels(KernelSet):
         the range of every batch row; made once per step on the device and kept with it for all layers."""
         made = step.derived.get("seq_index")
         if made is None:
-            rows = torch.arange(step.num_seqs + 1, dtype=torch.int32, device=self.device)
-            bounds = torch.searchsorted(step.token_seq, rows).to(torch.int32)
-            made = step.derived["seq_index"] = (bounds[step.token_seq.long()].contiguous(), bounds)
+            both = torch.empty(step.num_tokens + step.num_seqs + 1, dtype=torch.int32, device=self.device)
+            token_first, bounds = both[: step.num_tokens], both[step.num_tokens :]
+            check(
+                function("distie_seq_index")(step.token_seq.data_ptr(), step.num_tokens, step.num_seqs,
+                                             token_first.data_ptr(), bounds.data_ptr(), self._stream()),
+                "seq_index",
+            )
+            self._ran("seq_index")
+            made = step.derived["seq_index"] = (token_first, bounds)
         return made
 
     def short_conv(self, x, weight, bias, state, step, activation="silu"):
-        self._rows32(x, "short_conv")
+        sliced = self._sliced(x, "short_conv")
         channels, taps = weight.shape
         out = torch.empty((step.num_tokens, channels), dtype=torch.float32, device=x.device)
         single = step.num_decode_tokens == step.num_tokens  # one token per request: the kernel moves the state on itself
         token_first, seq_bounds = self._seq_index(step)
         check(
             function("distie_short_conv")(
-                x.data_ptr(), x.stride(0), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
+                *sliced, weight.data_ptr(), bias.data_ptr() if bias is not None else None,
                 state.data_ptr() if state is not None else None, step.token_seq.data_ptr(), token_first.data_ptr(),
                 seq_bounds.data_ptr(), step.seq_seat.data_ptr(), step.num_tokens, step.num_seqs, channels, taps, int(activation == "silu"), int(single), out.data_ptr(),
                 self._stream(),
@@ -547,14 +560,18 @@ class DeviceKernels(KernelSet):
 
     def linear_recurrence(self, rule, q, k, v, decay, write, state, step, heads, groups, key_dim, value_dim,
                           decay_rate=None, decay_bias=None, skip=None):
-        for name, t in (("q", q), ("k", k), ("v", v), ("decay", decay), ("write", write)):
+        for name, t in (("q", q), ("k", k), ("v", v)):
             self._rows32(t, f"linear_recurrence {name}")
+        decay_ptr, decay_stride, splits, split_stride = self._sliced(decay, "linear_recurrence decay")
+        write_ptr, write_stride, write_splits, write_split_stride = self._sliced(write, "linear_recurrence write")
+        if (splits, split_stride) != (write_splits, write_split_stride):
+            raise KernelError("linear_recurrence: decay and write are views of one projection")
         out = torch.empty((step.num_tokens, heads * value_dim), dtype=torch.float32, device=q.device)
         scratch = torch.empty(step.num_tokens * (2 * heads + groups), dtype=torch.float32, device=q.device)
         check(
             function("distie_linear_recurrence")(
                 _RULES[rule], q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
-                decay.data_ptr(), decay.stride(0), write.data_ptr(), write.stride(0), decay_rate.data_ptr(),
+                decay_ptr, decay_stride, write_ptr, write_stride, splits, split_stride, decay_rate.data_ptr(),
                 decay_bias.data_ptr() if decay_bias is not None else None, skip.data_ptr() if skip is not None else None,
                 state.data_ptr(), out.data_ptr(), out.stride(0), scratch.data_ptr(), self._seq_index(step)[1].data_ptr(),
                 step.seq_seat.data_ptr(), step.num_tokens, step.num_seqs, heads, groups, key_dim, value_dim,
@@ -567,10 +584,9 @@ class DeviceKernels(KernelSet):
 
     def gated_rmsnorm(self, x, gate, weight, eps, group, gate_first, out) -> None:
         self._rows32(x, "gated_rmsnorm x")
-        self._rows32(gate, "gated_rmsnorm gate")
         check(
             function("distie_gated_rmsnorm")(
-                x.data_ptr(), x.stride(0), gate.data_ptr(), gate.stride(0), weight.data_ptr(), weight.numel(),
+                x.data_ptr(), x.stride(0), *self._sliced(gate, "gated_rmsnorm gate"), weight.data_ptr(), weight.numel(),
                 out.data_ptr(), out.stride(0), x.shape[0], x.shape[1], group, float(eps), int(bool(gate_first)),
                 _CODE[out.dtype], self._stream(),
             ),

@@ -190,6 +190,8 @@ class KernelSet(ABC):
         dimension of ``kv.v`` and may differ from ``head_dim``; ``out`` is ``[T, heads * value size]``."""
 
     # -- layer norm, gates, short convolutions and linear recurrences (layers with per-request state) --------
+    # Where a float32 input is marked "or slices" it may also be ``[S, T, n]``, the slices of a split product
+    # (:meth:`linear_split`) or a view of their columns: the op adds them up while it loads.
     def add_layernorm(self, delta, residual, weight, bias, eps: float, out, rows_index=None) -> None:
         """residual += delta (float32, kept); out = (residual - mean) / sqrt(var + eps) * weight + bias, with the
         variance the mean of the squared deviations.  ``delta``: None, ``[T, hidden]``, float32 slices
@@ -202,11 +204,11 @@ class KernelSet(ABC):
         raise NotImplementedError
 
     def head_gate(self, x, logits, num_heads: int) -> None:
-        """x ``[T, heads * d]`` in place: head h of token t times sigmoid(logits[t, h]) (float32 logits)."""
+        """x ``[T, heads * d]`` in place: head h of token t times sigmoid(logits[t, h]) (float32 logits, or slices)."""
         raise NotImplementedError
 
     def short_conv(self, x, weight, bias, state, step: StepTensors, activation: str = "silu"):
-        """Causal convolution over time, per channel and per request: ``x [T, C]`` float32 (any row stride),
+        """Causal convolution over time, per channel and per request: ``x [T, C]`` float32 (any row stride; or slices),
         ``weight [C, taps]`` whose last column multiplies the current token, ``state [seats, taps - 1, C]`` the
         request's last inputs (oldest first; zeros at a request's start), which the call moves on by the
         step's tokens.  Returns float32 ``[T, C]`` after the activation (``"silu"`` or ``"none"``)."""
@@ -219,7 +221,7 @@ class KernelSet(ABC):
         ``S <- g S;  u = write-term;  S <- S + k u^T;  o = S^T q (+ skip * v)``
 
         Head h reads q and k of group ``h // (heads / groups)``.  ``q, k [T, groups * key_dim]``,
-        ``v [T, heads * value_dim]``, ``decay, write [T, heads]``, all float32 with any row stride.
+        ``v [T, heads * value_dim]``, ``decay, write [T, heads]`` (or slices), all float32 with any row stride.
 
         ``rule="delta"``: q and k are made unit vectors per head first (``x / sqrt(sum x^2 + 1e-6)``, q also
         times ``key_dim**-0.5``); ``g = exp(-exp(decay_rate) * softplus(decay + decay_bias))``;
@@ -234,7 +236,7 @@ class KernelSet(ABC):
 
     def gated_rmsnorm(self, x, gate, weight, eps: float, group: int, gate_first: bool, out) -> None:
         """Root-mean-square norm over groups of ``group`` neighbouring columns of ``x [T, n]`` (float32) with
-        a SiLU gate: ``gate_first``: ``norm(x * silu(gate)) * weight``; else ``norm(x) * weight * silu(gate)``.
+        a SiLU gate (float32, or slices): ``gate_first``: ``norm(x * silu(gate)) * weight``; else ``norm(x) * weight * silu(gate)``.
         ``weight`` is float32 of ``n`` elements, or fewer, then repeated (``weight[column % len]``)."""
         raise NotImplementedError
 

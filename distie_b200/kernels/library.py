@@ -46,12 +46,13 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     ),
     "distie_add_layernorm": ("state", [P, P, I, P, P, P, P, P, I, I, F, I, P]),
     "distie_kv_write": ("state", [P, I, P, I, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P, P]),
-    "distie_head_gate": ("state", [P, P, I, I, I, I, I, P]),
-    "distie_short_conv": ("state", [P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),
+    "distie_head_gate": ("state", [P, P, I, I, L, I, I, I, I, P]),
+    "distie_seq_index": ("state", [P, I, I, P, P, P]),
+    "distie_short_conv": ("state", [P, I, I, L, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),
     "distie_linear_recurrence": (
-        "state", [I, P, I, P, I, P, I, P, I, P, I, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, P]
+        "state", [I, P, I, P, I, P, I, P, I, P, I, I, L, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, P]
     ),
-    "distie_gated_rmsnorm": ("state", [P, I, P, I, P, I, P, I, I, I, I, F, I, I, P]),
+    "distie_gated_rmsnorm": ("state", [P, I, P, I, I, L, P, I, P, I, I, I, I, F, I, I, P]),
     "distie_gemm_tcgen05": ("bf16", [P, I, P, P, I, I, I, I, I, I, I, P, P]),
     "distie_gemm_tcgen05_qkv": ("bf16", [P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P]),
     "distie_gemm_tcgen05_skinny_splits": ("bf16", [I, I, I]),

@@ -166,7 +166,7 @@ class GqaAttention:
             k.qkv_attention(x, self.qkv.weight, self.qkv.bias, run.step, run.kv, run.writes_cache, table,
                             self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale, mixed, self.chunk)
         if self.gate is not None:
-            k.head_gate(mixed, k.linear(x, self.gate.weight, None, torch.float32), self.num_heads)
+            k.head_gate(mixed, k.linear_split(x, self.gate.weight), self.num_heads)
         if self.out.bias is not None:
             return self.out(mixed)
         return k.linear_split(mixed, self.out.weight)  # summed by the norm that follows

@@ -101,21 +101,20 @@ class GatedDeltaRule:
     def forward(self, x: torch.Tensor, run: LayerRun):
         k = self.kernels
         qk, vv, heads = self.groups * self.key_dim, self.heads * self.value_dim, self.heads
-        y = k.linear(x, self.proj.weight, None, torch.float32)
+        # The projection stays float32 slices [S, T, n] (the accumulators of a product whose reduction was split over
+        # thread blocks, or one slice): what reads it adds the slices up on the way in.
+        y = k.linear_split(x, self.proj.weight)
         state = run.state
-        mixed = y[:, : 2 * qk + vv]
-        if self.taps > 1:
-            mixed = k.short_conv(mixed, self.conv, None, state["conv"], run.step, "silu")
-        else:
-            mixed = k.short_conv(mixed, self.conv, None, None, run.step, "silu")
+        mixed = k.short_conv(y[:, :, : 2 * qk + vv], self.conv, None, state["conv"] if self.taps > 1 else None,
+                             run.step, "silu")
         at = 2 * qk + vv
         read = k.linear_recurrence(
-            "delta", mixed[:, :qk], mixed[:, qk : 2 * qk], mixed[:, 2 * qk :], y[:, at + heads : at + 2 * heads],
-            y[:, at : at + heads], state["matrix"], run.step, heads, self.groups, self.key_dim, self.value_dim,
+            "delta", mixed[:, :qk], mixed[:, qk : 2 * qk], mixed[:, 2 * qk :], y[:, :, at + heads : at + 2 * heads],
+            y[:, :, at : at + heads], state["matrix"], run.step, heads, self.groups, self.key_dim, self.value_dim,
             decay_rate=self.vectors["A_log"], decay_bias=self.vectors["dt_bias"],
         )
         normed = torch.empty((x.shape[0], vv), dtype=x.dtype, device=x.device)
-        k.gated_rmsnorm(read, y[:, at + 2 * heads :], self.vectors["norm"], self.eps, self.value_dim, False, normed)
+        k.gated_rmsnorm(read, y[:, :, at + 2 * heads :], self.vectors["norm"], self.eps, self.value_dim, False, normed)
         return k.linear_split(normed, self.out.weight)
 
 
@@ -188,16 +187,16 @@ class Mamba2:
     def forward(self, x: torch.Tensor, run: LayerRun):
         k = self.kernels
         inner, gn, heads = self.heads * self.value_dim, self.groups * self.n, self.heads
-        y = k.linear(x, self.proj.weight, None, torch.float32)
+        y = k.linear_split(x, self.proj.weight)  # float32 slices [S, T, n], added up by what reads them
         state = run.state
-        mixed = k.short_conv(y[:, inner : 2 * inner + 2 * gn], self.conv, self.conv_bias,
+        mixed = k.short_conv(y[:, :, inner : 2 * inner + 2 * gn], self.conv, self.conv_bias,
                              state["conv"] if self.taps > 1 else None, run.step, "silu")
-        dt = y[:, 2 * inner + 2 * gn :]
+        dt = y[:, :, 2 * inner + 2 * gn :]
         read = k.linear_recurrence(
             "ssd", mixed[:, inner + gn :], mixed[:, inner : inner + gn], mixed[:, :inner], dt, dt, state["matrix"],
             run.step, heads, self.groups, self.n, self.value_dim, decay_rate=self.vectors["A_log"],
             decay_bias=self.vectors["dt_bias"], skip=self.vectors["D"],
         )
         normed = torch.empty((x.shape[0], inner), dtype=x.dtype, device=x.device)
-        k.gated_rmsnorm(read, y[:, :inner], self.vectors["norm"], self.eps, inner // self.norm_groups, True, normed)
+        k.gated_rmsnorm(read, y[:, :, :inner], self.vectors["norm"], self.eps, inner // self.norm_groups, True, normed)
         return k.linear_split(normed, self.out.weight)

@@ -141,8 +141,14 @@ def kv_write(k, v, step: StepTensors, kv: KvSlot):
     kv.v[pages, :, pos % kv.page_size, :] = v[:tokens].reshape(tokens, kv.v.shape[1], kv.v.shape[3]).to(kv.v.dtype)
 
 
+def whole(x):
+    """A float32 matrix, or the sum of the slices ``[S, T, n]`` it was handed over as."""
+    return x.float().sum(0) if x.dim() == 3 else x.float()
+
+
 def head_gate(x, logits, num_heads):
     tokens = x.shape[0]
+    logits = whole(logits)
     gated = x.float().reshape(tokens, num_heads, -1) * torch.sigmoid(logits.float())[:, :, None]
     return gated.reshape(tokens, -1).to(x.dtype)
 
@@ -158,6 +164,7 @@ def _softplus(z):
 def short_conv(x, weight, bias, state, step: StepTensors, activation="silu"):
     """Token by token in the step's order: the request's window of inputs lives in ``state[seat]``."""
     tokens, taps = step.num_tokens, weight.shape[1]
+    x = whole(x)
     seats = token_seats(step)
     out = torch.zeros((tokens, x.shape[1]), dtype=torch.float32, device=x.device)
     for t in range(tokens):
@@ -177,6 +184,7 @@ def short_conv(x, weight, bias, state, step: StepTensors, activation="silu"):
 def linear_recurrence(rule, q, k, v, decay, write, state, step: StepTensors, heads, groups, key_dim, value_dim,
                       decay_rate=None, decay_bias=None, skip=None):
     tokens = step.num_tokens
+    decay, write = whole(decay), whole(write)
     seats = token_seats(step)
     out = torch.zeros((tokens, heads * value_dim), dtype=torch.float32, device=q.device)
     rep = heads // groups
@@ -210,7 +218,7 @@ def linear_recurrence(rule, q, k, v, decay, write, state, step: StepTensors, hea
 
 def gated_rmsnorm(x, gate, weight, eps, group, gate_first, dtype):
     tokens, n = x.shape
-    xf, gf = x.float(), _silu(gate.float())
+    xf, gf = x.float(), _silu(whole(gate))
     w = weight.float().repeat(n // weight.numel())
     if gate_first:
         xf = xf * gf

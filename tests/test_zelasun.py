@@ -234,6 +234,11 @@ def step_for(kit, entries):
     return views(torch.from_numpy(layout.packed).to(kit.device), layout)[0], layout
 
 
+def in_slices(x: torch.Tensor) -> torch.Tensor:
+    """``x`` as three slices ``[3, T, n]`` whose sum it is exactly (halves and quarters), as a split product leaves it."""
+    return torch.stack([x * 0.5, x * 0.25, x * 0.25])
+
+
 def _close(have, want, tol, what):
     scale = float(want.double().abs().max()) or 1.0
     err = float((have.double().cpu() - want.double()).abs().max()) / scale
@@ -279,7 +284,8 @@ def test_short_conv_in_portions_against_the_whole(kit, taps, channels):
         step, layout = step_for(kit, entries)
         rows = torch.cat([x[sl.seat][sl.past_len : sl.past_len + sl.q_len] for sl in layout.seqs])
         padded = torch.cat([rows, torch.zeros(rows.shape[0], 4)], dim=1).to(dev)  # a view with a row stride
-        out = kit.short_conv(padded[:, :channels], weight.to(dev), bias.to(dev), state, step, "silu")
+        given = padded[:, :channels] if taps != 4 else in_slices(padded)[:, :, :channels]  # a matrix, or slices of one
+        out = kit.short_conv(given, weight.to(dev), bias.to(dev), state, step, "silu")
         for sl in layout.seqs:
             got[sl.seat].append(out[sl.start : sl.start + sl.q_len].cpu())
             done[sl.seat] += sl.q_len
@@ -321,6 +327,9 @@ def test_linear_recurrence_in_portions_against_the_whole(kit, rule, heads, group
         step, layout = step_for(kit, [(s, [0] * n, done[s], ()) for s, n in cut])
         cat = {key: torch.cat([data[sl.seat][key][sl.past_len : sl.past_len + sl.q_len] for sl in layout.seqs]).to(dev)
                for key in "qkvdw"}
+        if value_dim % 2 == 0:  # decay and write as slices of a split product
+            both = in_slices(torch.cat([cat["d"], cat["w"]], dim=1))
+            cat["d"], cat["w"] = both[:, :, :heads], both[:, :, heads:]
         out = kit.linear_recurrence(rule, cat["q"], cat["k"], cat["v"], cat["d"], cat["w"], state, step, heads, groups,
                                     key_dim, value_dim, decay_rate=rate.to(dev), decay_bias=bias.to(dev),
                                     skip=skip.to(dev) if rule == "ssd" else None)
@@ -347,7 +356,8 @@ def test_gated_rmsnorm(kit, gate_first, group, weight_len):
         want = pz.rms_unit(xd.reshape(tokens, n // group, group), 1e-5).reshape(tokens, n) * full * gd
     dev = kit.device
     out = torch.empty(tokens, n, dtype=kit.dtype, device=dev)
-    kit.gated_rmsnorm(x.to(dev), gate.to(dev), weight.to(dev), 1e-5, group, gate_first, out)
+    kit.gated_rmsnorm(x.to(dev), in_slices(gate.to(dev)) if gate_first else gate.to(dev), weight.to(dev), 1e-5, group,
+                      gate_first, out)
     _close(out, want, 1e-5 if kit.dtype == torch.float32 else 2e-2, "gated norm")
 
 
@@ -409,6 +419,9 @@ def test_head_gate(kit):
     have = x.to(dev, kit.dtype).contiguous()
     kit.head_gate(have, logits.to(dev)[:, 2:8], 6)
     _close(have, want, 1e-6 if kit.dtype == torch.float32 else 1e-2, "head gate")
+    again = x.to(dev, kit.dtype).contiguous()
+    kit.head_gate(again, in_slices(logits.to(dev))[:, :, 2:8], 6)
+    _close(again, want, 1e-6 if kit.dtype == torch.float32 else 1e-2, "head gate from slices")
 
 
 # -- the whole model through the engine's step function -----------------------------------------------------
