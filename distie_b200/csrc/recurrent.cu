@@ -340,14 +340,14 @@ __global__ void short_conv_state_kernel(Sliced x, float* __restrict__ state,
 // Two kernels.  The first is parallel over tokens: it makes what a token contributes without the state
 // (per head g and the factor of u; per group k . q; for the delta rule q and k as unit vectors, in place).
 // The second walks the tokens.  The columns of S (one per value element) never meet, so a column belongs
-// to a group of eight lanes that share its key_dim entries (lane l holds i = 4 l + 32 r + c), and a block
-// of 64 threads owns 8 columns of one head of one request.  The read-out is taken from the state before the
+// to a group of 8, 16 or 32 lanes that share its key_dim entries (lane l of L holds i = 4 l + 4 L r + c), and a
+// block of 64 threads owns 8, 4 or 2 columns of one head of one request.  The read-out is taken from the state before the
 // write, o = g (S^T q) + u (k . q), which is the same number: both sums over the state then run side by side
 // instead of one after the other.  Tokens come in tiles of 16 that cp.async brings into shared memory a tile
 // ahead of the walk.
 // ---------------------------------------------------------------------------
 constexpr int kRuleDelta = 0, kRuleSsd = 1;
-constexpr int kScanThreads = 64, kScanColumns = 8, kScanTile = 16;
+constexpr int kScanThreads = 64, kScanTile = 16;
 
 struct ScanArgs {
   float *q, *k;  // the delta rule normalises them in place
@@ -420,17 +420,22 @@ template <int KD>
 struct ScanStage {
   float q[kScanTile][KD];
   float k[kScanTile][KD];
-  float v[kScanTile][kScanColumns];
+  float v[kScanTile][8];  // at most eight columns a block
   float g[kScanTile], factor[kScanTile], kq[kScanTile];
 };
 
-template <int PER, int RULE, bool VEC>
+// KD: key_dim rounded up (32, 64, 128, 256).  LANES: threads that share a column (8, 16 or 32; each holds
+// KD / LANES entries of it).  Few lanes mean few instructions per token and suit a step with many requests; many
+// lanes shorten each thread's chain of dependent instructions and fill the machine when one long prompt is all there is.
+template <int KD, int LANES, int RULE, bool VEC>
 __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArgs a) {
-  constexpr int KD = 8 * PER;
+  constexpr int PER = KD / LANES;
+  constexpr int kScanColumns = kScanThreads / LANES;
+  static_assert(PER >= 4 && PER % 4 == 0, "a thread holds whole float4s of its column");
   extern __shared__ __align__(16) unsigned char scan_smem[];
   ScanStage<KD>* stages = reinterpret_cast<ScanStage<KD>*>(scan_smem);  // two
   const int row = blockIdx.x, head = blockIdx.y;
-  const int tid = threadIdx.x, lane8 = tid & 7, col_local = tid >> 3;
+  const int tid = threadIdx.x, lane8 = tid % LANES, col_local = tid / LANES;
   const int j = blockIdx.z * kScanColumns + col_local;
   const bool valid = j < a.value_dim;
   const int grp = head / (a.heads / a.groups);
@@ -480,7 +485,7 @@ __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArg
   for (int r = 0; r < PER / 4; ++r)
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      const int i = 4 * lane8 + 32 * r + c;
+      const int i = 4 * lane8 + 4 * LANES * r + c;
       S[4 * r + c] = (valid && i < a.key_dim) ? column[i] : 0.f;
     }
   const float skip = (RULE == kRuleSsd && a.skip) ? a.skip[head] : 0.f;
@@ -497,8 +502,8 @@ __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArg
       float kk[PER], qq[PER];
 #pragma unroll
       for (int r = 0; r < PER / 4; ++r) {
-        const float4 kv = *reinterpret_cast<const float4*>(&st.k[tok][4 * lane8 + 32 * r]);
-        const float4 qv = *reinterpret_cast<const float4*>(&st.q[tok][4 * lane8 + 32 * r]);
+        const float4 kv = *reinterpret_cast<const float4*>(&st.k[tok][4 * lane8 + 4 * LANES * r]);
+        const float4 qv = *reinterpret_cast<const float4*>(&st.q[tok][4 * lane8 + 4 * LANES * r]);
         kk[4 * r] = kv.x; kk[4 * r + 1] = kv.y; kk[4 * r + 2] = kv.z; kk[4 * r + 3] = kv.w;
         qq[4 * r] = qv.x; qq[4 * r + 1] = qv.y; qq[4 * r + 2] = qv.z; qq[4 * r + 3] = qv.w;
       }
@@ -512,7 +517,7 @@ __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArg
       }
       float sum_k = (dk[0] + dk[1]) + (dk[2] + dk[3]), sum_q = (dq[0] + dq[1]) + (dq[2] + dq[3]);
 #pragma unroll
-      for (int offset = 1; offset < 8; offset <<= 1) {
+      for (int offset = 1; offset < LANES; offset <<= 1) {
         if (RULE == kRuleDelta) sum_k += __shfl_xor_sync(0xffffffffu, sum_k, offset);
         sum_q += __shfl_xor_sync(0xffffffffu, sum_q, offset);
       }
@@ -529,23 +534,39 @@ __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArg
     for (int r = 0; r < PER / 4; ++r)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const int i = 4 * lane8 + 32 * r + c;
+        const int i = 4 * lane8 + 4 * LANES * r + c;
         if (i < a.key_dim) column[i] = S[4 * r + c];
       }
   }
 }
 
-template <int PER, int RULE>
+template <int KD, int LANES, int RULE>
 static cudaError_t launch_scan_sized(const ScanArgs& a, int num_seqs, bool vec, cudaStream_t stream) {
-  const dim3 grid(num_seqs, a.heads, (a.value_dim + kScanColumns - 1) / kScanColumns);
-  const size_t shared = 2 * sizeof(ScanStage<8 * PER>);
+  constexpr int columns = kScanThreads / LANES;
+  const dim3 grid(num_seqs, a.heads, (a.value_dim + columns - 1) / columns);
+  const size_t shared = 2 * sizeof(ScanStage<KD>);
   auto run = [&](auto kernel) {
     if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     kernel<<<grid, kScanThreads, shared, stream>>>(a);
   };
-  if (vec) run(linear_recurrence_kernel<PER, RULE, true>);
-  else run(linear_recurrence_kernel<PER, RULE, false>);
+  if (vec) run(linear_recurrence_kernel<KD, LANES, RULE, true>);
+  else run(linear_recurrence_kernel<KD, LANES, RULE, false>);
   return cudaGetLastError();
+}
+
+template <int KD, int RULE>
+static cudaError_t launch_scan_lanes(const ScanArgs& a, int num_seqs, bool vec, cudaStream_t stream) {
+  // Lanes per column: as few as keep the machine in warps (about ten to an SM), at most what leaves a thread a float4.
+  const long long columns = (long long)num_seqs * a.heads * a.value_dim;
+  int lanes = 8;
+  while (lanes < 32 && KD / (2 * lanes) >= 4 && columns * lanes / 32 < 1500) lanes *= 2;
+  if constexpr (KD >= 128) {
+    if (lanes == 32) return launch_scan_sized<KD, 32, RULE>(a, num_seqs, vec, stream);
+  }
+  if constexpr (KD >= 64) {
+    if (lanes == 16) return launch_scan_sized<KD, 16, RULE>(a, num_seqs, vec, stream);
+  }
+  return launch_scan_sized<KD, 8, RULE>(a, num_seqs, vec, stream);
 }
 
 template <int RULE>
@@ -556,10 +577,10 @@ static cudaError_t launch_scan(const ScanArgs& a, int num_seqs, cudaStream_t str
   // 16-byte copies need rows of q and k that start on 16-byte boundaries
   const bool vec = a.key_dim % 4 == 0 && a.q_stride % 4 == 0 && a.k_stride % 4 == 0 &&
                    (((uintptr_t)a.q | (uintptr_t)a.k) & 15) == 0;
-  if (a.key_dim <= 32) return launch_scan_sized<4, RULE>(a, num_seqs, vec, stream);
-  if (a.key_dim <= 64) return launch_scan_sized<8, RULE>(a, num_seqs, vec, stream);
-  if (a.key_dim <= 128) return launch_scan_sized<16, RULE>(a, num_seqs, vec, stream);
-  return launch_scan_sized<32, RULE>(a, num_seqs, vec, stream);
+  if (a.key_dim <= 32) return launch_scan_lanes<32, RULE>(a, num_seqs, vec, stream);
+  if (a.key_dim <= 64) return launch_scan_lanes<64, RULE>(a, num_seqs, vec, stream);
+  if (a.key_dim <= 128) return launch_scan_lanes<128, RULE>(a, num_seqs, vec, stream);
+  return launch_scan_lanes<256, RULE>(a, num_seqs, vec, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -797,7 +818,7 @@ extern "C" int distie_linear_recurrence(int rule, float* q, int q_stride, float*
   if (tokens <= 0) return 0;
   if (heads < 1 || groups < 1 || heads % groups || key_dim < 1 || value_dim < 1 || num_seqs < 1 || heads > 65535)
     return DISTIE_ERR_ARG;
-  if (key_dim > 256 || (value_dim + kScanColumns - 1) / kScanColumns > 65535) return DISTIE_ERR_UNSUPPORTED;
+  if (key_dim > 256 || (value_dim + 1) / 2 > 65535) return DISTIE_ERR_UNSUPPORTED;
   if (rate == nullptr || state == nullptr || scratch == nullptr || (rule == kRuleDelta && decay == nullptr))
     return DISTIE_ERR_ARG;
   ScanArgs a;

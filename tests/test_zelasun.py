@@ -297,6 +297,9 @@ def test_short_conv_in_portions_against_the_whole(kit, taps, channels):
 @pytest.mark.parametrize("rule,heads,groups,key_dim,value_dim", [
     ("delta", 4, 2, 16, 8), ("delta", 2, 2, 40, 20), ("delta", 3, 1, 160, 18), ("delta", 1, 1, 128, 33),
     ("ssd", 4, 2, 16, 8), ("ssd", 3, 1, 20, 12), ("ssd", 2, 2, 64, 40), ("ssd", 1, 1, 200, 5),
+    # many columns: the kernel then gives a column fewer lanes
+    ("delta", 48, 2, 128, 128), ("ssd", 24, 1, 100, 64), ("delta", 24, 4, 256, 64), ("ssd", 64, 1, 64, 64),
+    ("ssd", 48, 2, 256, 128),
 ])
 def test_linear_recurrence_in_portions_against_the_whole(kit, rule, heads, groups, key_dim, value_dim):
     g = torch.Generator().manual_seed(key_dim)
@@ -416,10 +419,10 @@ def test_head_gate(kit):
     x, logits = torch.randn(7, 6 * 10, generator=g), torch.randn(7, 9, generator=g) * 3
     want = (x.double().reshape(7, 6, 10) * torch.sigmoid(logits.double()[:, 2:8, None])).reshape(7, 60)
     dev = kit.device
-    have = x.to(dev, kit.dtype).contiguous()
+    have = x.clone().to(dev, kit.dtype).contiguous()
     kit.head_gate(have, logits.to(dev)[:, 2:8], 6)
     _close(have, want, 1e-6 if kit.dtype == torch.float32 else 1e-2, "head gate")
-    again = x.to(dev, kit.dtype).contiguous()
+    again = x.clone().to(dev, kit.dtype).contiguous()
     kit.head_gate(again, in_slices(logits.to(dev))[:, :, 2:8], 6)
     _close(again, want, 1e-6 if kit.dtype == torch.float32 else 1e-2, "head gate from slices")
 
