@@ -421,7 +421,7 @@ struct ScanStage {
   float q[kScanTile][KD];
   float k[kScanTile][KD];
   float v[kScanTile][8];  // at most eight columns a block
-  float g[kScanTile], factor[kScanTile], kq[kScanTile];
+  float scalars[kScanTile][4];  // per token: g, the factor of u, k . q, unused
 };
 
 // KD: key_dim rounded up (32, 64, 128, 256).  LANES: threads that share a column (8, 16 or 32; each holds
@@ -471,9 +471,9 @@ __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArg
     if (tid < count) {
       const bool live = true;
       const size_t t = tile + tid;
-      cp_async_f1(&st.g[tid], a.scalars + (t * a.heads + head) * 2, live);
-      cp_async_f1(&st.factor[tid], a.scalars + (t * a.heads + head) * 2 + 1, live);
-      cp_async_f1(&st.kq[tid], a.kq + t * a.groups + grp, live);
+      cp_async_f1(&st.scalars[tid][0], a.scalars + (t * a.heads + head) * 2, live);
+      cp_async_f1(&st.scalars[tid][1], a.scalars + (t * a.heads + head) * 2 + 1, live);
+      cp_async_f1(&st.scalars[tid][2], a.kq + t * a.groups + grp, live);
     }
     cp_async_commit();
   };
@@ -498,6 +498,8 @@ __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArg
     if (more) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();
     const ScanStage<KD>& st = stages[buffer];
+    float* out_at = a.out + (size_t)tile * a.out_stride + head * a.value_dim + (valid ? j : 0);
+#pragma unroll 4
     for (int tok = 0; tok < count; ++tok) {
       float kk[PER], qq[PER];
 #pragma unroll
@@ -507,7 +509,8 @@ __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArg
         kk[4 * r] = kv.x; kk[4 * r + 1] = kv.y; kk[4 * r + 2] = kv.z; kk[4 * r + 3] = kv.w;
         qq[4 * r] = qv.x; qq[4 * r + 1] = qv.y; qq[4 * r + 2] = qv.z; qq[4 * r + 3] = qv.w;
       }
-      const float g = st.g[tok], vj = st.v[tok][col_local];
+      const float4 per_token = *reinterpret_cast<const float4*>(st.scalars[tok]);
+      const float g = per_token.x, factor = per_token.y, kq = per_token.z, vj = st.v[tok][col_local];
       // S^T k and S^T q of this column before the write, four partial sums each
       float dk[4] = {0.f, 0.f, 0.f, 0.f}, dq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -521,11 +524,10 @@ __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArg
         if (RULE == kRuleDelta) sum_k += __shfl_xor_sync(0xffffffffu, sum_k, offset);
         sum_q += __shfl_xor_sync(0xffffffffu, sum_q, offset);
       }
-      const float u = RULE == kRuleDelta ? st.factor[tok] * (vj - g * sum_k) : st.factor[tok] * vj;
+      const float u = RULE == kRuleDelta ? factor * (vj - g * sum_k) : factor * vj;
 #pragma unroll
       for (int e = 0; e < PER; ++e) S[e] = g * S[e] + kk[e] * u;
-      if (lane8 == 0 && valid)
-        a.out[(size_t)(tile + tok) * a.out_stride + head * a.value_dim + j] = g * sum_q + u * st.kq[tok] + skip * vj;
+      if (lane8 == 0 && valid) out_at[(size_t)tok * a.out_stride] = g * sum_q + u * kq + skip * vj;
     }
     __syncthreads();  // everyone is done with this stage before the copies of the tile after next land in it
   }
@@ -556,10 +558,10 @@ static cudaError_t launch_scan_sized(const ScanArgs& a, int num_seqs, bool vec, 
 
 template <int KD, int RULE>
 static cudaError_t launch_scan_lanes(const ScanArgs& a, int num_seqs, bool vec, cudaStream_t stream) {
-  // Lanes per column: as few as keep the machine in warps (about ten to an SM), at most what leaves a thread a float4.
+  // Lanes per column: as few as keep the machine in warps (about four to an SM), at most what leaves a thread a float4.
   const long long columns = (long long)num_seqs * a.heads * a.value_dim;
   int lanes = 8;
-  while (lanes < 32 && KD / (2 * lanes) >= 4 && columns * lanes / 32 < 1500) lanes *= 2;
+  while (lanes < 32 && KD / (2 * lanes) >= 4 && columns * lanes / 32 < 600) lanes *= 2;
   if constexpr (KD >= 128) {
     if (lanes == 32) return launch_scan_sized<KD, 32, RULE>(a, num_seqs, vec, stream);
   }

@@ -298,7 +298,7 @@ def test_short_conv_in_portions_against_the_whole(kit, taps, channels):
     ("delta", 4, 2, 16, 8), ("delta", 2, 2, 40, 20), ("delta", 3, 1, 160, 18), ("delta", 1, 1, 128, 33),
     ("ssd", 4, 2, 16, 8), ("ssd", 3, 1, 20, 12), ("ssd", 2, 2, 64, 40), ("ssd", 1, 1, 200, 5),
     # many columns: the kernel then gives a column fewer lanes
-    ("delta", 48, 2, 128, 128), ("ssd", 24, 1, 100, 64), ("delta", 24, 4, 256, 64), ("ssd", 64, 1, 64, 64),
+    ("delta", 48, 2, 128, 128), ("ssd", 12, 1, 100, 64), ("delta", 12, 4, 256, 64), ("ssd", 64, 1, 64, 64),
     ("ssd", 48, 2, 256, 128),
 ])
 def test_linear_recurrence_in_portions_against_the_whole(kit, rule, heads, groups, key_dim, value_dim):
