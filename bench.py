@@ -30,7 +30,9 @@ contexts, prefill of 2,048 tokens); ``--shape 7b`` is ``configs[3]``, the mixed
 continuous-batching run through ``Engine.generate`` (64 requests, prompts of 64 to 2,048
 tokens, 256 outputs each, 2,048-token step budget, 32 seats) with time to first token,
 time per output token, preemptions and the step-time split; ``--dtype fp32`` times the
-true 32-bit engine.  Their caches are sized from free device memory.
+true 32-bit engine.  Their caches are sized from free device memory.  ``--compare zelasun`` times the
+Zelasun design beside the Qwen2 decoder at equal width, feed-forward, heads and depth (prefill of 2,048
+tokens, decode steps at ``--batch``; the time of a layer from two depths) and prints a line of its own.
 """
 
 from __future__ import annotations

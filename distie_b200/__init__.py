@@ -1,4 +1,5 @@
-"""distie_b200: a single-GPU inference engine for the Qwen2 dense decoder on B200 (sm_100a).
+"""distie_b200: a single-GPU inference engine on B200 (sm_100a) for the Qwen2 dense decoder and the Zelasun
+hybrid decoder (chunked attention beside a gated delta rule, and Mamba-2 layers).
 
 From a model folder (``config.json`` + safetensors) to generated tokens: typed
 configuration and architecture registry, weights by tensor name, layers composed
