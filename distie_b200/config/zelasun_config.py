@@ -144,7 +144,7 @@ class ZelasunConfig:
                 mixer = Mamba2Sizes.read(sizes, where + "mixer.")
             else:
                 raise ConfigError(f"{where}type {kind!r}: this design has 'parallel' and 'mamba2' layers")
-            mlp = _get(entry, "mlp", where)
+            mlp = entry.get("mlp")  # null, or absent: the layer has no feed-forward
             ff = None
             if mlp is not None:
                 if _get(mlp, "kind", where + "mlp.") != "dense":

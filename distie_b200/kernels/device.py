@@ -524,6 +524,10 @@ class DeviceKernels(KernelSet):
         )
         self._ran("head_gate")
 
+    def prepare_step(self, step) -> None:
+        """What several sublayers of a block share of the step, made before they part onto streams of their own."""
+        self._seq_index(step)
+
     def _seq_index(self, step):
         """(token_first [T], seq_bounds [B + 1]), int32: where each token's request starts among the step's tokens and
         the range of every batch row; made once per step on the device and kept with it for all layers."""

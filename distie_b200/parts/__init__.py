@@ -6,6 +6,7 @@ from .base import (
     MIXERS,
     NORMS,
     POSITION_ENCODINGS,
+    Branches,
     BuildContext,
     CacheNeed,
     LayerRun,
@@ -23,6 +24,7 @@ __all__ = [
     "MIXERS",
     "NORMS",
     "POSITION_ENCODINGS",
+    "Branches",
     "BuildContext",
     "CacheNeed",
     "LayerRun",

@@ -139,6 +139,41 @@ class ResidualStream:
         return self.residual
 
 
+class Branches:
+    """Sublayers of a block that read the same input and do not read one another: run side by side.
+
+    On a CUDA device a step of few tokens is a chain of short kernels, each waiting for the one before; the
+    branches of a parallel block (two mixers and a feed-forward) are independent chains, so each gets a stream
+    of its own between a fork after the block's norm and a join before the next kernel of the main stream.
+    A captured decode step records the fork and the join as edges of its graph.  Every tensor a branch makes
+    and hands back is read only after the join and before the next fork, and what it frees returns to its own
+    stream's pool, so no block of memory is reused while another stream may still read it.  Steps of many tokens
+    fill the machine with every kernel and stay on one stream.
+    """
+
+    SMALL_STEP = 64
+    _side: dict = {}
+
+    @classmethod
+    def run(cls, jobs, tokens: int, device: torch.device) -> list:
+        if len(jobs) < 2 or device.type != "cuda" or tokens > cls.SMALL_STEP:
+            return [job() for job in jobs]
+        streams = cls._side.setdefault(str(device), [])
+        while len(streams) < len(jobs) - 1:
+            streams.append(torch.cuda.Stream(device=device))
+        main = torch.cuda.current_stream(device)
+        results = [None] * len(jobs)
+        for index, job in enumerate(jobs[1:], start=1):
+            side = streams[index - 1]
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                results[index] = job()
+        results[0] = jobs[0]()
+        for side in streams[: len(jobs) - 1]:
+            main.wait_stream(side)
+        return results
+
+
 # -- registries ---------------------------------------------------------------
 class Registry:
     def __init__(self, what: str) -> None:

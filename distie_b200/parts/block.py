@@ -16,7 +16,7 @@ import torch
 
 from ..config.model_spec import LayerSpec
 from ..kernels.interface import Terms
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildContext, LayerRun, ResidualStream, TensorSpec, build_part
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Branches, BuildContext, LayerRun, ResidualStream, TensorSpec, build_part
 
 
 @BLOCKS.register("pre_norm")
@@ -67,11 +67,12 @@ class PreNormBlock:
 class ParallelBlock:
     """norms: ``input`` only.  A feed-forward of kind ``none`` adds nothing."""
 
-    def __init__(self, norm_in, mixer, feed_forward, dtype) -> None:
+    def __init__(self, norm_in, mixer, feed_forward, dtype, kernels=None) -> None:
         self.norm_in = norm_in
         self.mixer = mixer
         self.feed_forward = feed_forward
         self.dtype = dtype
+        self.kernels = kernels
 
     @property
     def graph_safe(self) -> bool:
@@ -92,12 +93,24 @@ class ParallelBlock:
             build_part(MIXERS, layer.mixer, ctx),
             build_part(FEED_FORWARDS, layer.feed_forward, ctx),
             ctx.dtype,
+            ctx.kernels,
         )
 
     def forward(self, stream: ResidualStream, run: LayerRun) -> None:
         residual = stream.residual
         x = torch.empty(residual.shape, dtype=self.dtype, device=residual.device)
         self.norm_in.apply(stream.pending, residual, x)
-        pending = Terms.of(self.mixer.forward(x, run))
-        fed = self.feed_forward.forward(x, run)
-        stream.pending = pending if fed is None else pending + Terms.of(fed)
+        # What the sublayers share of the step (where each request's tokens lie) is made before they part.
+        prepare = getattr(self.kernels, "prepare_step", None)
+        if prepare is not None:
+            prepare(run.step)
+        # The mixer's branches (one, or the two of a pair side by side) and the feed-forward read x and nothing of
+        # one another: in a step of few tokens they run side by side.
+        jobs = list(self.mixer.branches(x, run)) if hasattr(self.mixer, "branches") else [lambda: self.mixer.forward(x, run)]
+        if not isinstance(self.feed_forward, FEED_FORWARDS.get("none")):
+            jobs.append(lambda: self.feed_forward.forward(x, run))
+        outputs = Branches.run(jobs, x.shape[0], x.device)
+        pending = Terms.of(outputs[0])
+        for more in outputs[1:]:
+            pending = pending + Terms.of(more)
+        stream.pending = pending

@@ -73,7 +73,13 @@ class SideBySide:
         own = {name[len(side) + 1 :]: t for name, t in state.items() if name.startswith(side + ".")}
         return own or None
 
+    def branches(self, x: torch.Tensor, run: LayerRun):
+        """The two mixers as jobs that a block may run side by side; each returns its weighted output."""
+        left_run = replace(run, state=self._state_of(run.state, "left"))
+        right_run = replace(run, state=self._state_of(run.state, "right"))
+        return (lambda: Terms.of(self.left.forward(x, left_run), self.left_scale),
+                lambda: Terms.of(self.right.forward(x, right_run), self.right_scale))
+
     def forward(self, x: torch.Tensor, run: LayerRun):
-        left = self.left.forward(x, replace(run, state=self._state_of(run.state, "left")))
-        right = self.right.forward(x, replace(run, state=self._state_of(run.state, "right")))
-        return Terms.of(left, self.left_scale) + Terms.of(right, self.right_scale)
+        left, right = (job() for job in self.branches(x, run))
+        return left + right

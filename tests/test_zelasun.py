@@ -266,6 +266,15 @@ def test_layernorm_adds_a_weighted_sum_and_norms(kit, width):
     kit.add_layernorm(Terms([(a.to(dev), 0.6), (b.to(dev), 0.5)]), res2, weight.to(dev), bias.to(dev), 1e-5, picked, rows)
     _close(res2, residual, 0.0, "residual kept")
     _close(picked, want[[7, 2]], 1e-5 if kit.dtype == torch.float32 else 2e-2, "picked rows")
+    # more terms than the kernel's argument list holds: the slices of three deep products
+    many = [torch.randn(11, tokens, width, generator=g) for _ in range(3)]
+    want_res = residual.double() + sum(scale * m.double().sum(0) for scale, m in zip((0.5, 1.0, -0.25), many))
+    res3 = residual.clone().to(dev)
+    kit.add_layernorm(Terms([(m.to(dev), scale) for scale, m in zip((0.5, 1.0, -0.25), many)]), res3, weight.to(dev),
+                      bias.to(dev), 1e-5, out)
+    _close(res3, want_res, 2e-6, "residual after 33 terms")
+    _close(out, pz.layer_norm(want_res, weight.double(), bias.double(), 1e-5), 1e-5 if kit.dtype == torch.float32 else 2e-2,
+           "norm after 33 terms")
 
 
 @pytest.mark.parametrize("taps,channels", [(4, 37), (2, 130), (1, 8), (7, 16), (4, 64), (3, 260)])
@@ -504,6 +513,8 @@ def test_long_decoding_keeps_the_state(kit):
     got = helpers.collect(steps, helpers.run_schedule(TraceSession(engine), steps))
     want_other = plain_logits(cfg, weights, other)[3::4]
     assert_close(got, {"long": plain_logits(cfg, weights, long_ids), "o0": want_other, "o1": want_other}, tolerance(kit), "long")
+    if kit.device.type == "cuda":  # steps of single tokens replayed the captured decode step, state and all
+        assert engine.runner.use_graphs and engine.runner.graph_replays >= 100
 
 
 @pytest.mark.parametrize("name", ["small", "awkward", "no_pages"])
