@@ -313,6 +313,61 @@ __global__ void short_conv_vec_kernel(Sliced x, const float* __restrict__ weight
   *reinterpret_cast<float4*>(out + (size_t)t * channels + c) = acc;
 }
 
+// Four taps, four channels and a run of eight tokens a thread, the window of held inputs in registers: every input
+// is loaded once instead of once per tap, and a block lives eight times as long.  A run that crosses from one
+// request into the next falls back to the token-by-token form.
+constexpr int kConvRun = 8;
+__global__ void short_conv_run4_kernel(Sliced x, const float* __restrict__ weight, const float* __restrict__ bias,
+                                       const float* __restrict__ state, const int* __restrict__ token_seq,
+                                       const int* __restrict__ token_first, const int* __restrict__ seq_seat, int tokens,
+                                       int channels, int silu, float* __restrict__ out) {
+  const int t0 = blockIdx.y * kConvRun;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (c >= channels) return;
+  const int n = min(kConvRun, tokens - t0);
+  float4 w[4];  // w[j]: tap j of the four channels (tap 3 multiplies the current token)
+  {
+    const float4 a = *reinterpret_cast<const float4*>(weight + (size_t)c * 4), b = *reinterpret_cast<const float4*>(weight + (size_t)(c + 1) * 4);
+    const float4 d = *reinterpret_cast<const float4*>(weight + (size_t)(c + 2) * 4), e = *reinterpret_cast<const float4*>(weight + (size_t)(c + 3) * 4);
+    w[0] = make_float4(a.x, b.x, d.x, e.x); w[1] = make_float4(a.y, b.y, d.y, e.y);
+    w[2] = make_float4(a.z, b.z, d.z, e.z); w[3] = make_float4(a.w, b.w, d.w, e.w);
+  }
+  const float4 base = bias ? *reinterpret_cast<const float4*>(bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  auto input = [&](int at, int first, const float* held) {  // the input at token index `at` of a request that starts at `first`
+    if (at >= first) return x.at4(at, c);
+    if (held) return *reinterpret_cast<const float4*>(held + (size_t)(at - first + 3) * channels + c);
+    return make_float4(0.f, 0.f, 0.f, 0.f);
+  };
+  auto finish = [&](int t, float4 acc) {
+    if (silu) acc = make_float4(silu_f(acc.x), silu_f(acc.y), silu_f(acc.z), silu_f(acc.w));
+    *reinterpret_cast<float4*>(out + (size_t)t * channels + c) = acc;
+  };
+  auto mac = [](float4 acc, float4 wj, float4 v) {
+    return make_float4(acc.x + wj.x * v.x, acc.y + wj.y * v.y, acc.z + wj.z * v.z, acc.w + wj.w * v.w);
+  };
+  const int row0 = token_seq[t0];
+  if (row0 == token_seq[t0 + n - 1]) {
+    const int first = token_first[t0];
+    const float* held = state ? state + (size_t)seq_seat[row0] * 3 * channels : nullptr;
+    float4 back3 = input(t0 - 3, first, held), back2 = input(t0 - 2, first, held), back1 = input(t0 - 1, first, held);
+#pragma unroll
+    for (int k = 0; k < kConvRun; ++k) {
+      if (k < n) {
+        const float4 now = x.at4(t0 + k, c);
+        finish(t0 + k, mac(mac(mac(mac(base, w[0], back3), w[1], back2), w[2], back1), w[3], now));
+        back3 = back2; back2 = back1; back1 = now;
+      }
+    }
+  } else {
+    for (int k = 0; k < n; ++k) {
+      const int t = t0 + k, first = token_first[t];
+      const float* held = state ? state + (size_t)seq_seat[token_seq[t]] * 3 * channels : nullptr;
+      finish(t, mac(mac(mac(mac(base, w[0], input(t - 3, first, held)), w[1], input(t - 2, first, held)), w[2],
+                        input(t - 1, first, held)), w[3], x.at4(t, c)));
+    }
+  }
+}
+
 __global__ void short_conv_state_kernel(Sliced x, float* __restrict__ state,
                                         const int* __restrict__ seq_bounds, const int* __restrict__ seq_seat,
                                         int channels, int taps) {
@@ -783,7 +838,11 @@ extern "C" int distie_short_conv(const float* x_ptr, int x_stride, int splits, l
                    (((uintptr_t)x_ptr | (uintptr_t)state | (uintptr_t)out | (uintptr_t)bias) & 15) == 0;
   if (vec) {
     const dim3 grid((channels / 4 + threads - 1) / threads, tokens);
-    if (taps == 4)
+    if (taps == 4 && ((uintptr_t)weight & 15) == 0) {
+      const dim3 grid_runs(grid.x, (tokens + kConvRun - 1) / kConvRun);
+      short_conv_run4_kernel<<<grid_runs, threads, 0, stream>>>(x, weight, bias, state, token_seq, token_first, seq_seat,
+                                                                tokens, channels, silu, out);
+    } else if (taps == 4)
       short_conv_vec_kernel<4><<<grid, threads, 0, stream>>>(x, weight, bias, state, token_seq, token_first,
                                                              seq_seat, channels, taps, silu, out);
     else
