@@ -543,3 +543,57 @@ def test_greedy_generation_through_the_scheduler(kit, name):
             best = float(logits[index].max())
             slack = (2e-4 if kit.dtype == torch.float32 else 8e-2) * float(logits[index].std())
             assert float(logits[index, token]) >= best - slack, f"{result.request_id}: output {index} is no arg-max"
+
+
+# -- the command line and the trace runner, as a user runs them ---------------------------------------------
+@pytest.mark.gpu
+def test_command_line_and_trace_runner(tmp_path):
+    """``init-random`` writes a Zelasun folder from its configuration file, ``generate`` decodes greedily from it and
+    ``bin/trace_run`` replays steps against it (a portion, then portions beside single tokens, then an ended request's
+    seat used again): tokens and logits are the plain implementation's."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    from distie_b200.weights import ModelTensors
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    config_file = tmp_path / "cfg.json"
+    config_file.write_text(json.dumps(SMALL))
+    folder = tmp_path / "model"
+    subprocess.run([sys.executable, "-m", "distie_b200", "init-random", "--config", str(config_file), "--out", str(folder),
+                    "--seed", "9", "--std", "0.3", "--dtype", "bfloat16"], check=True, env=env, cwd=root, timeout=600)
+    stored = ModelTensors(str(folder))
+    weights = {name: stored.tensor(name).float() for name in stored.keys()}
+    prompt = helpers.random_ids(SMALL["vocab"], 19, 41)
+    proc = subprocess.run([sys.executable, "-m", "distie_b200", "generate", "--model", str(folder), "--dtype", "fp32",
+                           "--prompt", " ".join(map(str, prompt)), "--max-new-tokens", "8", "--num-blocks", "8",
+                           "--ignore-eos"], capture_output=True, text=True, env=env, cwd=root, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    tokens = json.loads(proc.stdout)[0]["token_ids"]
+    logits = plain_logits(SMALL, weights, prompt + tokens[:-1])[len(prompt) - 1 :]
+    for index, token in enumerate(tokens):
+        assert float(logits[index, token]) >= float(logits[index].max()) - 2e-4 * float(logits[index].std())
+
+    a, b = helpers.random_ids(SMALL["vocab"], 40, 42), helpers.random_ids(SMALL["vocab"], 30, 43)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:25], "want": [0, 24]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[25:26], "want": [0]}, {"id": "b", "tokens": b[:7], "want": [6]}], "end": []},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[7:], "want": [22]}, {"id": "a", "tokens": a[26:], "want": [13]}], "end": ["a", "b"]},
+        {"step": 3, "entries": [{"id": "c", "tokens": b, "want": [29]}], "end": ["c"]},
+    ]
+    out = tmp_path / "out"
+    proc = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(out),
+                           "--max-tokens", "128"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True,
+                          text=True, env=env, cwd=root, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [line for line in proc.stdout.splitlines() if line.startswith("done")] == [f"done {i}" for i in range(4)]
+    full_a, full_b = plain_logits(SMALL, weights, a), plain_logits(SMALL, weights, b)
+    want = {0: full_a[[0, 24]], 1: torch.stack([full_a[25], full_b[6]]), 2: torch.stack([full_b[29], full_a[39]]), 3: full_b[[29]]}
+    for step, rows in want.items():
+        got = torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(rows.shape))
+        assert float(row_errors(got, rows).max()) <= FP32_TOL, f"step {step}"
