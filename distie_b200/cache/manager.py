@@ -24,6 +24,9 @@ values live in one device slab per group, indexed by those ids.
   several by name), zeroed when a seat is opened and when a request is sent back to be
   recomputed.  Layers with a recurrence keep their matrix state and the last inputs of
   their short convolutions here.
+* A windowed group whose need names ``keep_first`` keeps the pages that hold the request's first
+  that-many positions for as long as the request lives: ``trim`` gives back only the pages between them
+  and the window.
 * A group whose need names a ``chunk`` gives pages back like a windowed one: no later
   position reads a key from before the chunk the request is in.  A group whose values
   have another size than its keys keeps two slabs instead of one.
@@ -67,10 +70,13 @@ def pages_that_fit(cache_needs, page_size: int, element_size: int, budget_bytes:
 class _SeatPages:
     first: int = 0   # logical index of the first page still held
     ids: list | None = None  # page ids of logical pages first, first + 1, ...
+    kept: list | None = None  # page ids of logical pages 0, 1, ... that are held for good, once pages behind them went back
 
     def __post_init__(self) -> None:
         if self.ids is None:
             self.ids = []
+        if self.kept is None:
+            self.kept = []
 
 
 class KvGroup:
@@ -140,6 +146,11 @@ class KvGroup:
         if held is None or (self.need.window is None and self.need.chunk is None):
             return 0
         keep_from = min(self.first_needed_page(cached), held.first + len(held.ids))
+        head = pages_needed(int(self.need.keep_first), self.page_size) if self.need.window is not None else 0
+        if head and held.first == 0 and not held.kept:
+            if keep_from <= head:
+                return 0  # nothing lies between the pages kept for good and the window yet
+            held.kept, held.ids, held.first = held.ids[:head], held.ids[head:], head
         drop = keep_from - held.first
         if drop <= 0:
             return 0
@@ -155,15 +166,15 @@ class KvGroup:
         held = self.seats.pop(seat, None)
         if held is None:
             return
-        if held.ids:
-            self.pool.free(held.ids)
+        if held.ids or held.kept:
+            self.pool.free(held.kept + held.ids)
         self._before_write()
         self.host_table[seat, :] = -1
         self._mark(seat, 0)
 
     def pages_of(self, seat: int) -> list[int]:
         held = self.seats.get(seat)
-        return list(held.ids) if held else []
+        return held.kept + held.ids if held else []
 
     # -- device side --------------------------------------------------------
     def allocate_device(self, dtype: torch.dtype, device: torch.device) -> None:

@@ -3,6 +3,7 @@
 from .engine_config import EngineConfig, resolve_dtype_name
 from .model_spec import LayerCall, LayerSpec, ModelSpec, PartSpec
 from .qwen2_config import ConfigError, Qwen2Config
+from .fovudra_config import FovudraConfig
 from .zelasun_config import ZelasunConfig
 from .registry import (
     Architecture,
@@ -18,6 +19,7 @@ __all__ = [
     "Architecture",
     "ConfigError",
     "EngineConfig",
+    "FovudraConfig",
     "LayerCall",
     "LayerSpec",
     "ModelSpec",

@@ -70,6 +70,7 @@ class ModelSpec:
     init: Mapping[str, float] = field(default_factory=dict)  # hints for random weights
     # Constants some architectures put around the stack of layers; all off (None) for the plain decoder.
     embedding_scale: float | None = None  # the embedded tokens are multiplied by it
+    embedding_norm: PartSpec | None = None  # a norm of the embedded tokens; what it returns starts the residual
     logit_scale: float | None = None      # the logits are multiplied by it
     logit_softcap: float | None = None    # then logits = cap * tanh(logits / cap)
 

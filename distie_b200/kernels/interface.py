@@ -17,7 +17,8 @@ Shapes (``T`` tokens of this step, ``B`` requests of this step):
     block_table [seats, width] int32
 
 Which keys a token sees: all keys up to its own position (``first_visible``), the last
-``window`` of them, or those of its own ``chunk`` (positions ``chunk * n .. chunk * (n + 1) - 1``).
+``window`` of them, or those of its own ``chunk`` (positions ``chunk * n .. chunk * (n + 1) - 1``);
+beside a window, the request's first ``keep_first`` positions when a layer keeps them.
 """
 
 from __future__ import annotations
@@ -99,6 +100,19 @@ class Terms:
             part = tensor if scale == 1.0 else tensor * scale
             total = part if total is None else total + part
         return total
+
+
+@dataclass
+class Normed:
+    """A sublayer's output that is normalised before it joins the residual: ``rms_norm(sum of terms) * weight``.
+
+    ``value`` is what a mixer or feed-forward returns (a matrix, float32 slices or :class:`Terms`); ``weight`` is
+    the float32 scale of the norm (an offset the checkpoint leaves out is already added) and ``eps`` its epsilon.
+    The norm kernel that follows does the sum, this norm, the addition to the residual and its own norm in one pass."""
+
+    value: object
+    weight: torch.Tensor
+    eps: float
 
 
 @dataclass(frozen=True)
@@ -184,10 +198,66 @@ class KernelSet(ABC):
 
     @abstractmethod
     def attention(self, qkv, out, step: StepTensors, kv: KvSlot, num_heads: int, num_kv_heads: int,
-                  head_dim: int, window: int | None, scale: float, chunk: int | None = None) -> None:
+                  head_dim: int, window: int | None, scale: float, chunk: int | None = None,
+                  keep_first: int = 0) -> None:
         """Causal attention of every token over its request's pages, optionally only over the last
-        ``window`` keys or over the keys of the token's own ``chunk``.  The size of a value is the last
-        dimension of ``kv.v`` and may differ from ``head_dim``; ``out`` is ``[T, heads * value size]``."""
+        ``window`` keys or over the keys of the token's own ``chunk``.  With a window, ``keep_first`` keeps
+        the request's first that-many positions visible to every later token, at their true positions.
+        The size of a value is the last dimension of ``kv.v`` and may differ from ``head_dim``; ``out`` is
+        ``[T, heads * value size]``."""
+
+    # -- norms around a sublayer, keys that are their own values, routed feed-forwards -----------------------------
+    def norm_add_rmsnorm(self, delta, delta_weight, delta_eps: float, residual, weight, eps: float, out,
+                         rows_index=None) -> None:
+        """``d = sum of delta's terms`` (float32); ``residual += d * rsqrt(mean(d^2) + delta_eps) * delta_weight``
+        (kept); ``out = cast(residual * rsqrt(mean(residual^2) + eps) * weight)``, everything in float32 up to the
+        one cast.  ``delta``: None (nothing is added), a matrix, float32 slices or :class:`Terms`; with
+        ``delta_weight`` None the sum is added as it is.  With ``rows_index`` only those rows are made and the
+        residual stays as it is.  ``out`` None: only the residual is moved on."""
+        raise NotImplementedError
+
+    def qk_rope_norm_write(self, qk, bias, step: StepTensors, kv: KvSlot | None, rotary: RotaryTable | None,
+                           num_heads: int, num_kv_heads: int, head_dim: int, norm_eps: float | None, q_out) -> None:
+        """For layers whose values are their keys: ``qk`` is the projection ``[T, (heads + kv_heads) * head_dim]``
+        (float32, or the float32 slices of a split product) and ``bias`` its float32 bias or None.  The key with
+        its bias, before anything else is done to it, is stored as the value; q and k are rotated (``rotary``),
+        then, with ``norm_eps`` not None, each head is divided by its root mean square over ``head_dim``; k goes to
+        its page (if ``kv``) and q to ``q_out [T, heads * head_dim]`` in the set's dtype.  All arithmetic float32."""
+        raise NotImplementedError
+
+    def activation(self, x, kind: str = "silu", scale: float = 1.0, scaled_columns: int = 0):
+        """A float32 matrix ``[T, n]`` out of ``x`` (float32, any row stride, or slices): ``act(x)`` with ``kind``
+        ``"silu"`` or ``"none"``, the first ``scaled_columns`` columns also times ``scale``."""
+        raise NotImplementedError
+
+    def exp_gate_scan(self, log_in, log_forget, in_bias, forget_bias, cap: float, state, step: StepTensors):
+        """Exponential gates with a running maximum, per head and request, float32:
+
+        ``i = cap * tanh((log_in + in_bias) / cap)``; ``f = logsigmoid(cap * tanh((log_forget + forget_bias) / cap))``;
+        ``m_t = max(f_t + m_(t-1), i_t)``; returns ``(keep, take, floor)``, each ``[T, heads]``:
+        ``keep = exp(f + m_(t-1) - m_t)``, ``take = exp(i - m_t)``, ``floor = exp(-m_t)``.
+        ``log_in, log_forget [T, heads]`` float32 (or slices); ``state [seats, heads]`` holds m (0 at a request's
+        start) and is moved on by the step's tokens."""
+        raise NotImplementedError
+
+    def stabilized_readout(self, read, floor, heads: int, value_dim: int):
+        """``read [T, heads * (value_dim + 1)]`` is the read-out of a recurrence whose last column per head is the
+        normaliser ``n . q``: returns float32 ``[T, heads * value_dim]`` with head h of token t divided by
+        ``max(|n . q|, floor[t, h]) + 1e-6``."""
+        raise NotImplementedError
+
+    def route_top(self, x, router, top: int, scoring: str = "sigmoid"):
+        """The ``top`` experts of every token: logits ``x @ router.T`` (``router [experts, hidden]``) accumulated in
+        float32 -> ``(ids [T, top] int32, weights [T, top] float32)``, ``weights`` the chosen experts' scores
+        (``sigmoid(logit)``, not renormalised), the largest first, ties to the lower index."""
+        raise NotImplementedError
+
+    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input: bool = True):
+        """Every token through its chosen experts: ``gate_up [experts, 2 ff, hidden]`` (gate rows, then up rows),
+        ``down [experts, hidden, ff]``; expert e of pair (t, j) computes ``down_e (silu(gate_e z) * (up_e z))`` with
+        ``z = weights[t, j] * x[t]`` (``scale_input``) or on ``x[t]`` with the result times the weight.  Returns
+        float32 slices ``[top, T, hidden]`` whose sum over the first axis is the routed output."""
+        raise NotImplementedError
 
     # -- layer norm, gates, short convolutions and linear recurrences (layers with per-request state) --------
     # Where a float32 input is marked "or slices" it may also be ``[S, T, n]``, the slices of a split product
@@ -215,7 +285,8 @@ class KernelSet(ABC):
         raise NotImplementedError
 
     def linear_recurrence(self, rule: str, q, k, v, decay, write, state, step: StepTensors, heads: int, groups: int,
-                          key_dim: int, value_dim: int, decay_rate=None, decay_bias=None, skip=None):
+                          key_dim: int, value_dim: int, decay_rate=None, decay_bias=None, skip=None,
+                          unit_column: bool = False):
         """A matrix state ``S [key_dim, value_dim]`` per head and request, moved on token by token in float32:
 
         ``S <- g S;  u = write-term;  S <- S + k u^T;  o = S^T q (+ skip * v)``
@@ -228,15 +299,20 @@ class KernelSet(ABC):
         ``u = sigmoid(write) * (v - S^T k)`` with the decayed S.
         ``rule="ssd"``: ``dt = softplus(write + decay_bias)``; ``g = exp(-exp(decay_rate) * dt)``; ``u = dt * v``;
         ``skip [heads]`` adds ``skip_h * v`` to the read-out (``decay`` is not read).
+        ``rule="gated"``: nothing is normalised; ``g = decay[t, h]`` as given, or with ``decay`` None the constant
+        ``decay_rate[h]``; ``u = write[t, h] * v``, or ``v`` with ``write`` None.  With ``unit_column`` the state has
+        one more column per head than ``v`` has elements (``value_dim`` counts it), whose value is 1 for every
+        token: it carries ``n <- g n + write k`` and its read-out ``n . q`` is the last column of each head.
 
         ``state`` is ``[seats, heads, value_dim, key_dim]`` float32 (S transposed), read and written through
         each token's seat.  Returns float32 ``[T, heads * value_dim]``.  A set may overwrite ``q`` and ``k``
         (with their unit vectors): the caller hands over buffers it no longer needs."""
         raise NotImplementedError
 
-    def gated_rmsnorm(self, x, gate, weight, eps: float, group: int, gate_first: bool, out) -> None:
+    def gated_rmsnorm(self, x, gate, weight, eps: float, group: int, gate_first: bool, out,
+                      activation: str = "silu") -> None:
         """Root-mean-square norm over groups of ``group`` neighbouring columns of ``x [T, n]`` (float32) with
-        a SiLU gate (float32, or slices): ``gate_first``: ``norm(x * silu(gate)) * weight``; else ``norm(x) * weight * silu(gate)``.
+        a gate (float32, or slices; written ``silu`` below, ``activation="sigmoid"`` makes it ``sigmoid(gate)``): ``gate_first``: ``norm(x * silu(gate)) * weight``; else ``norm(x) * weight * silu(gate)``.
         ``weight`` is float32 of ``n`` elements, or fewer, then repeated (``weight[column % len]``)."""
         raise NotImplementedError
 

@@ -5,7 +5,7 @@ it is given, against the cache slots the step's :class:`CacheView` hands out, an
 returns float32 logits at the wanted rows (embedding -> layers -> row select ->
 final norm -> head, the order of worker/src/inference/qwen2/model.py:369-380).
 A spec may put constants around the stack (a scale on the embedded tokens, a scale
-and a soft cap on the logits); the architecture built here sets none of them.
+and a soft cap on the logits, a norm of the embedded tokens); the reference's architecture sets none of them.
 """
 
 from __future__ import annotations
@@ -23,6 +23,8 @@ from ..parts.linear import Linear
 def model_tensor_specs(spec: ModelSpec) -> list[TensorSpec]:
     """Every tensor the model reads, in a fixed order (also the order random weights are drawn in)."""
     specs = [TensorSpec(spec.embedding_name, (spec.vocab_size, spec.hidden_size), "table")]
+    if spec.embedding_norm is not None:
+        specs += NORMS.get(spec.embedding_norm.kind).tensor_specs(spec.embedding_norm, spec.hidden_size)
     for layer in spec.layers:
         specs += BLOCKS.get(layer.block).tensor_specs(layer, spec.hidden_size)
     specs += NORMS.get(spec.final_norm.kind).tensor_specs(spec.final_norm, spec.hidden_size)
@@ -61,6 +63,7 @@ class DecoderModel:
         self.kernels = kernels
         ctx = BuildContext(kernels, spec.hidden_size, weights)
         self.embedding = weights.table(spec.embedding_name)
+        self.embedding_norm = build_part(NORMS, spec.embedding_norm, ctx) if spec.embedding_norm is not None else None
         self.blocks = [BLOCKS.get(layer.block).build(layer, ctx) for layer in spec.layers]
         self.final_norm = build_part(NORMS, spec.final_norm, ctx)
         head = self.embedding if spec.head_name is None else weights.table(spec.head_name)
@@ -88,6 +91,7 @@ class DecoderModel:
 
         visit(self.blocks)
         visit(self.final_norm)
+        visit(self.embedding_norm)
         visit(self.head)
         return sum(seen.values())
 
@@ -98,6 +102,11 @@ class DecoderModel:
         if self.spec.embedding_scale is not None:
             residual.mul_(float(self.spec.embedding_scale))
         stream = ResidualStream(residual)
+        if self.embedding_norm is not None:
+            # The norm of the embedded tokens starts the residual: it stays pending on a residual of zeros, and the
+            # first block's norm kernel does both norms in one pass.
+            stream = ResidualStream(torch.zeros_like(residual), self.embedding_norm.pending(residual))
+            residual = stream.residual
         for call in self.spec.order:
             run = LayerRun(
                 step=step,

@@ -11,7 +11,10 @@ Beyond the reference: ``chunk`` (a token sees only the keys of its own chunk of 
 positions, counted from position 0 of the request), ``value_dim`` (values of another size than
 keys), ``gate="head_sigmoid"`` (a projection ``g`` of the mixer's input to one number per head;
 head h's output is multiplied by ``sigmoid(g_h)`` before the output projection) and ``names`` (what
-the tensors are called in the checkpoint).
+the tensors are called in the checkpoint; ``bias_suffix`` what a bias adds to its matrix's name), ``values="keys"``
+(no value projection: a token's value is its key as projected, bias included, before rotation and norm),
+``qk_norm`` (an epsilon: after the rotation every head of q and k is divided by its root mean square) and
+``keep_first`` (beside a window: the request's first positions stay visible to every later token).
 
 The three projections are one product against the row-stacked weight; rotation
 and cache write are one kernel; attention reads q from the same buffer.
@@ -30,7 +33,8 @@ from .linear import Linear, fuse_rows
 class GqaAttention:
     """params: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``qkv_bias``, ``out_bias``,
     ``window`` (None: full), ``chunk`` (None: none), ``value_dim`` (None: ``head_dim``), ``gate`` (None or
-    ``"head_sigmoid"``), ``scale`` (None: ``head_dim**-0.5``), ``position`` (a PartSpec), ``names``.
+    ``"head_sigmoid"``), ``scale`` (None: ``head_dim**-0.5``), ``position`` (a PartSpec), ``names``, ``bias_suffix``,
+    ``values`` (``"projected"`` or ``"keys"``), ``qk_norm`` (None or an epsilon), ``keep_first`` (0).
 
     tensors: ``q_proj``/``k_proj``/``v_proj``/``o_proj`` ``.weight`` (and ``.bias``), ``g_proj.weight`` with a
     gate; ``names`` maps ``q, k, v, o, g`` to other names (biases then add ``.bias`` to the stem).
@@ -50,6 +54,9 @@ class GqaAttention:
         self.value_dim = int(params.get("value_dim") or self.head_dim)
         self.window = params.get("window")
         self.chunk = params.get("chunk")
+        self.keep_first = int(params.get("keep_first") or 0)
+        self.values_are_keys = params.get("values", "projected") == "keys"
+        self.qk_norm = params.get("qk_norm")
         self.scale = float(params.get("scale") or self.head_dim**-0.5)
         self.kernels = kernels
 
@@ -58,7 +65,7 @@ class GqaAttention:
         name = spec.prefix + spec.params.get("names", cls._NAMES).get(which, cls._NAMES[which])
         if not bias:
             return name
-        return (name[: -len(".weight")] if name.endswith(".weight") else name) + ".bias"
+        return (name[: -len(".weight")] if name.endswith(".weight") else name) + spec.params.get("bias_suffix", ".bias")
 
     # -- declarations -------------------------------------------------------
     @staticmethod
@@ -74,6 +81,14 @@ class GqaAttention:
                 raise ValueError(f"{key} must be >= 1, got {params[key]}")
         if params.get("gate") not in (None, "head_sigmoid"):
             raise ValueError(f"gate {params['gate']!r}: None or 'head_sigmoid'")
+        if params.get("values", "projected") not in ("projected", "keys"):
+            raise ValueError(f"values {params['values']!r}: 'projected' or 'keys'")
+        if params.get("values") == "keys" and vdim != dim:
+            raise ValueError("values that are the keys have the keys' size")
+        if params.get("qk_norm") is not None and params.get("values") != "keys":
+            raise ValueError("qk_norm goes with values='keys' (the op that rotates, norms and stores in one pass)")
+        if int(params.get("keep_first") or 0) < 0 or (params.get("keep_first") and not params.get("window")):
+            raise ValueError("keep_first is a non-negative count and goes with a window")
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, hidden_size: int) -> list[TensorSpec]:
@@ -83,11 +98,13 @@ class GqaAttention:
         q_out = prm["num_heads"] * prm["head_dim"]
         kv_out = prm["num_kv_heads"] * prm["head_dim"]
         v_out = prm["num_kv_heads"] * vdim
+        own_values = prm.get("values", "projected") != "keys"
         specs = [
             TensorSpec(cls._name(spec, "q"), (q_out, hidden_size)),
             TensorSpec(cls._name(spec, "k"), (kv_out, hidden_size)),
-            TensorSpec(cls._name(spec, "v"), (v_out, hidden_size)),
         ]
+        if own_values:
+            specs.append(TensorSpec(cls._name(spec, "v"), (v_out, hidden_size)))
         if prm.get("gate"):
             specs.append(TensorSpec(cls._name(spec, "g"), (prm["num_heads"], hidden_size)))
         specs.append(TensorSpec(cls._name(spec, "o"), (hidden_size, prm["num_heads"] * vdim)))
@@ -95,8 +112,9 @@ class GqaAttention:
             specs += [
                 TensorSpec(cls._name(spec, "q", True), (q_out,), "bias"),
                 TensorSpec(cls._name(spec, "k", True), (kv_out,), "bias"),
-                TensorSpec(cls._name(spec, "v", True), (v_out,), "bias"),
             ]
+            if own_values:
+                specs.append(TensorSpec(cls._name(spec, "v", True), (v_out,), "bias"))
         if prm.get("out_bias", False):
             specs.append(TensorSpec(cls._name(spec, "o", True), (hidden_size,), "bias"))
         return specs
@@ -106,7 +124,7 @@ class GqaAttention:
         prm = spec.params
         vdim = int(prm.get("value_dim") or prm["head_dim"])
         return CacheNeed(int(prm["num_kv_heads"]), int(prm["head_dim"]), prm.get("window"), prm.get("chunk"),
-                         vdim if vdim != int(prm["head_dim"]) else None)
+                         vdim if vdim != int(prm["head_dim"]) else None, int(prm.get("keep_first") or 0))
 
     @classmethod
     def state_need(cls, spec: PartSpec):
@@ -116,8 +134,9 @@ class GqaAttention:
     def build(cls, spec: PartSpec, ctx: BuildContext) -> "GqaAttention":
         cls._check(spec.params)
         prm, w = spec.params, ctx.weights
-        weight = fuse_rows([w.matrix(cls._name(spec, n)) for n in "qkv"])
-        bias = fuse_rows([w.vector(cls._name(spec, n, True)) for n in "qkv"]) if prm.get("qkv_bias", False) else None
+        stacked = "qkv" if prm.get("values", "projected") != "keys" else "qk"
+        weight = fuse_rows([w.matrix(cls._name(spec, n)) for n in stacked])
+        bias = fuse_rows([w.vector(cls._name(spec, n, True)) for n in stacked]) if prm.get("qkv_bias", False) else None
         out_bias = w.vector(cls._name(spec, "o", True)) if prm.get("out_bias", False) else None
         position = build_part(POSITION_ENCODINGS, prm.get("position") or PartSpec("none"), ctx)
         gate = Linear(w.matrix(cls._name(spec, "g")), None, ctx.kernels) if prm.get("gate") else None
@@ -137,7 +156,20 @@ class GqaAttention:
         k = self.kernels
         mixed = torch.empty((x.shape[0], self.num_heads * self.value_dim), dtype=x.dtype, device=x.device)
         table = self.position.rotary_table()
-        if self.value_dim != self.head_dim:
+        if self.values_are_keys:
+            # One projection [q | k]; what follows it (bias, the key kept as the value, rotation, the norm of every
+            # head, the stores into the pages and of q) is one op on the product's float32 accumulators.
+            if table is None and hasattr(self.position, "apply"):
+                raise RuntimeError("values that are the keys go with a rotary table or no rotation")
+            q = torch.empty((x.shape[0], self.num_heads * self.head_dim), dtype=x.dtype, device=x.device)
+            k.qk_rope_norm_write(k.linear_split(x, self.qkv.weight), self.qkv.bias, run.step,
+                                 run.kv if run.writes_cache else None, table, self.num_heads, self.num_kv_heads,
+                                 self.head_dim, self.qk_norm, q)
+            k.attention(q, mixed, run.step, run.kv, self.num_heads, self.num_kv_heads, self.head_dim, self.window,
+                        self.scale, self.chunk, self.keep_first)
+        elif self.keep_first:
+            raise RuntimeError("keep_first is served for values='keys' layers only")
+        elif self.value_dim != self.head_dim:
             # Values of another size than keys: nothing of the fused kernels fits; the projection is finished,
             # keys and values go to their pages as they are (such layers rotate nothing) and the size-agnostic
             # attention reads q from the projection's first columns.

@@ -32,7 +32,7 @@ from typing import Any, Callable, Sequence
 import torch
 
 from ..config.model_spec import PartSpec
-from ..kernels.interface import KernelSet, KvSlot, StepTensors, Terms
+from ..kernels.interface import KernelSet, KvSlot, Normed, StepTensors, Terms
 
 
 # -- what parts declare --------------------------------------------------------
@@ -44,6 +44,7 @@ class TensorSpec:
     ``table``   embedding table (like ``matrix``)
     ``bias``    vector added to a product (kept in float32 on the device)
     ``norm``    scale of a norm (float32 on the device; random mode writes ones)
+    ``norm0``   scale of a norm that is stored around zero (the norm multiplies by 1 + it; random mode writes zeros)
     """
 
     name: str
@@ -60,6 +61,7 @@ class CacheNeed:
     window: int | None = None  # None: every key is kept; n: only the last n positions are read
     chunk: int | None = None   # n: a token reads only keys of its own chunk of n positions (counted from 0)
     value_dim: int | None = None  # size of a value when it differs from head_dim
+    keep_first: int = 0        # beside a window: the request's first n positions stay readable for good
 
     @property
     def v_dim(self) -> int:
@@ -129,6 +131,11 @@ class ResidualStream:
         self.pending = pending
 
     def settle(self) -> torch.Tensor:
+        if isinstance(self.pending, Normed):  # a sublayer's output that joins the residual through a norm
+            value = ResidualStream(torch.zeros_like(self.residual), self.pending.value).settle()
+            unit = value * torch.rsqrt((value * value).mean(-1, keepdim=True) + self.pending.eps)
+            self.residual.add_(unit * self.pending.weight)
+            self.pending = None
         if self.pending is not None:
             if isinstance(self.pending, Terms):
                 delta = self.pending.total()

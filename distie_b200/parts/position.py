@@ -4,7 +4,10 @@
 ``inv_freq[j] = 1 / theta**(2j / d)`` computed in float32 exactly as there, angles
 ``pos * inv_freq`` and their cos/sin evaluated in float32 inside the fused kernel,
 pairs ``(j, j + d/2)`` (rotate-half).  ``rotary_dim < head_dim``, interleaved pairs and
-a factor on cos and sin are parameters for other layer kinds.  ``none`` rotates nothing.
+a factor on cos and sin are parameters for other layer kinds, and so is ``scaling``, which divides the
+frequencies of long waves: with wavelength ``l = 2 pi / f``, ``f`` stays where ``l < original / high``, becomes
+``f / factor`` where ``l > original / low``, and in between ``(1 - s) f / factor + s f`` with
+``s = (original / l - low) / (high - low)``.  ``none`` rotates nothing.
 
 An encoding that is no table of frequencies (learned or additive positions, a rotation
 that depends on more than the position) returns ``None`` from ``rotary_table()`` and
@@ -14,6 +17,8 @@ place, and the fused kernel then only stores the keys and values.
 """
 
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -27,9 +32,20 @@ from .base import POSITION_ENCODINGS, BuildContext
 _TABLES: dict[tuple, RotaryTable] = {}
 
 
+def scaled_frequencies(theta: float, rotary_dim: int, factor: float, low: float, high: float, original: float) -> torch.Tensor:
+    """Rotary frequencies ``theta**(-2j / d)`` with the long waves slowed down, made in float64 and stored as float32."""
+    freq = theta ** (-torch.arange(0, rotary_dim, 2, dtype=torch.float64) / rotary_dim)
+    wavelength = 2.0 * math.pi / freq
+    blend = ((original / wavelength - low) / (high - low)).clamp(0.0, 1.0)
+    mixed = (1.0 - blend) * freq / factor + blend * freq
+    out = torch.where(wavelength < original / high, freq, torch.where(wavelength > original / low, freq / factor, mixed))
+    return out.to(torch.float32)
+
+
 @POSITION_ENCODINGS.register("rotary")
 class RotaryEncoding:
-    """params: ``head_dim``, ``theta``, optional ``rotary_dim``, ``interleaved``, ``factor``."""
+    """params: ``head_dim``, ``theta``, optional ``rotary_dim``, ``interleaved``, ``factor``, ``scaling``
+    (a mapping with ``factor``, ``low``, ``high``, ``original``)."""
 
     def __init__(self, table: RotaryTable) -> None:
         self._table = table
@@ -41,11 +57,16 @@ class RotaryEncoding:
         theta = float(spec.params["theta"])
         if rotary_dim % 2 or rotary_dim > head_dim:
             raise ValueError(f"rotary_dim {rotary_dim} must be even and at most head_dim {head_dim}")
+        scaling = spec.params.get("scaling")
+        scaled = tuple(float(scaling[n]) for n in ("factor", "low", "high", "original")) if scaling else None
         key = (theta, rotary_dim, bool(spec.params.get("interleaved", False)), float(spec.params.get("factor", 1.0)),
-               str(ctx.device))
+               str(ctx.device), scaled)
         table = _TABLES.get(key)
         if table is None:
-            inv_freq = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
+            if scaled is None:
+                inv_freq = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
+            else:
+                inv_freq = scaled_frequencies(theta, rotary_dim, *scaled)
             table = _TABLES[key] = RotaryTable(inv_freq.to(ctx.device), *key[1:4])
         return cls(table)
 

@@ -117,7 +117,7 @@ class WeightStore:
         raw = self._source.tensor(name)
         if not raw.dtype.is_floating_point:
             target = torch.int32
-        elif role in ("bias", "norm"):
+        elif role in ("bias", "norm", "norm0"):
             target = torch.float32
         elif self.dtype == torch.float32 or (self.keep_wide and raw.dtype in _WIDE):
             target = torch.float32

@@ -4,7 +4,8 @@
 parts declare, under their checkpoint names, so that the ordinary loader reads the
 folder like any other.  Values come from one ``torch.Generator(seed)`` on the CPU,
 drawn in float32 in the declared order of the tensors and then cast: products'
-weights, tables and biases ``N(0, std)``, norm scales ``1 + N(0, norm_noise)``.
+weights, tables and biases ``N(0, std)``, norm scales ``1 + N(0, norm_noise)`` (``N(0, norm_noise)`` for a
+scale that is stored around zero).
 ``std`` defaults to the configuration's ``initializer_range`` when it has one.
 """
 
@@ -27,8 +28,8 @@ def random_tensors(specs, seed: int, std: float, norm_noise: float, dtype: torch
     for spec in specs:
         if spec.name in out:
             continue
-        if spec.role == "norm":
-            value = torch.ones(spec.shape)
+        if spec.role in ("norm", "norm0"):
+            value = torch.ones(spec.shape) if spec.role == "norm" else torch.zeros(spec.shape)
             if norm_noise:
                 value = value + torch.randn(spec.shape, generator=generator) * norm_noise
         else:
@@ -64,8 +65,8 @@ class RandomSource:
     def tensor(self, name):
         spec, index = self._specs[name]
         generator = torch.Generator(device=self.device).manual_seed(self.seed * 1_000_003 + index)
-        if spec.role == "norm":
-            value = torch.ones(spec.shape, device=self.device)
+        if spec.role in ("norm", "norm0"):
+            value = (torch.ones if spec.role == "norm" else torch.zeros)(spec.shape, device=self.device)
             if self.norm_noise:
                 value += torch.randn(spec.shape, generator=generator, device=self.device) * self.norm_noise
         else:

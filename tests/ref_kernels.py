@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import torch
 
-from distie_b200.kernels.interface import KernelSet, KvSlot, RotaryTable, StepTensors, Terms
+from distie_b200.kernels.interface import KernelSet, KvSlot, Normed, RotaryTable, StepTensors, Terms
 
 
 def embed(ids, table):
@@ -87,7 +87,8 @@ def rope_kv_write(qkv, step: StepTensors, kv: KvSlot | None, rotary, num_heads, 
     kv.v[pages, :, pos % kv.page_size, :] = v
 
 
-def attention(qkv, step: StepTensors, kv: KvSlot, num_heads, num_kv_heads, head_dim, window, scale, chunk=None):
+def attention(qkv, step: StepTensors, kv: KvSlot, num_heads, num_kv_heads, head_dim, window, scale, chunk=None,
+              keep_first=0):
     """Token by token: gather the visible keys of the token's request from its pages, softmax in float32."""
     tokens = step.num_tokens
     out = torch.zeros((tokens, num_heads * kv.v.shape[-1]), dtype=qkv.dtype, device=qkv.device)
@@ -99,6 +100,8 @@ def attention(qkv, step: StepTensors, kv: KvSlot, num_heads, num_kv_heads, head_
         if chunk:
             first = max(first, pos // int(chunk) * int(chunk))
         keys = torch.arange(first, pos + 1, device=qkv.device)
+        if keep_first and first > 0:  # the request's first positions stay visible beside the window
+            keys = torch.cat([torch.arange(0, min(int(keep_first), first), device=qkv.device), keys])
         pages = kv.block_table[seat, keys // kv.page_size].long()
         if bool(((pages < 0) | (pages >= kv.num_pages)).any()):
             raise IndexError("a block table does not cover the keys a token attends to")
@@ -216,9 +219,9 @@ def linear_recurrence(rule, q, k, v, decay, write, state, step: StepTensors, hea
     return out
 
 
-def gated_rmsnorm(x, gate, weight, eps, group, gate_first, dtype):
+def gated_rmsnorm(x, gate, weight, eps, group, gate_first, dtype, activation="silu"):
     tokens, n = x.shape
-    xf, gf = x.float(), _silu(whole(gate))
+    xf, gf = x.float(), (_silu(whole(gate)) if activation == "silu" else torch.sigmoid(whole(gate)))
     w = weight.float().repeat(n // weight.numel())
     if gate_first:
         xf = xf * gf
@@ -227,6 +230,126 @@ def gated_rmsnorm(x, gate, weight, eps, group, gate_first, dtype):
     if not gate_first:
         normed = normed * gf
     return normed.to(dtype)
+
+
+def flat_sum(value):
+    """A pending value (None, a matrix, float32 slices or Terms) as one float32 matrix."""
+    if value is None:
+        return None
+    if isinstance(value, Terms):
+        return value.total()
+    return value.float().sum(0) if value.dim() == 3 else value.float()
+
+
+def norm_add_rmsnorm(delta, delta_weight, delta_eps, residual, weight, eps, dtype, rows_index=None):
+    """Returns (new residual, normed)."""
+    d = flat_sum(delta)
+    if d is not None and delta_weight is not None:
+        d = d * torch.rsqrt((d * d).mean(-1, keepdim=True) + delta_eps) * delta_weight.float()
+    summed = residual if d is None else residual + d
+    source = summed if rows_index is None else summed[rows_index.long()]
+    out = (source * torch.rsqrt((source * source).mean(-1, keepdim=True) + eps) * weight.float()).to(dtype)
+    return (summed if rows_index is None else residual), out
+
+
+def qk_rope_norm_write(qk, bias, step: StepTensors, kv: KvSlot | None, rotary, num_heads, num_kv_heads, head_dim,
+                       norm_eps, q_dtype):
+    """Returns q [T, heads * head_dim]; stores k (rotated, normed) and v (the key as projected) in their pages."""
+    tokens = step.num_tokens
+    dense = whole(qk)[:tokens]
+    if bias is not None:
+        dense = dense + bias.float()
+    positions = step.positions[:tokens]
+    q = dense[:, : num_heads * head_dim].reshape(tokens, num_heads, head_dim)
+    k = dense[:, num_heads * head_dim :].reshape(tokens, num_kv_heads, head_dim)
+    v = k.clone()
+    q, k = rotate(q, positions, rotary), rotate(k, positions, rotary)
+    if norm_eps is not None:
+        q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + norm_eps)
+        k = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + norm_eps)
+    if kv is not None:
+        pos = positions.long()
+        pages = kv.block_table[token_seats(step), pos // kv.page_size].long()
+        if bool(((pages < 0) | (pages >= kv.num_pages)).any()):
+            raise IndexError("a new token's page is missing from its block table")
+        kv.k[pages, :, pos % kv.page_size, :] = k.to(kv.k.dtype)
+        kv.v[pages, :, pos % kv.page_size, :] = v.to(kv.v.dtype)
+    return q.reshape(tokens, num_heads * head_dim).to(q_dtype)
+
+
+def activation(x, kind="silu", scale=1.0, scaled_columns=0):
+    out = whole(x).clone()
+    if kind == "silu":
+        out = _silu(out)
+    if scaled_columns:
+        out[:, :scaled_columns] *= scale
+    return out
+
+
+def exp_gate_scan(log_in, log_forget, in_bias, forget_bias, cap, state, step: StepTensors):
+    tokens = step.num_tokens
+    i = cap * torch.tanh((whole(log_in)[:tokens] + in_bias.float()) / cap)
+    f = torch.nn.functional.logsigmoid(cap * torch.tanh((whole(log_forget)[:tokens] + forget_bias.float()) / cap))
+    seats = token_seats(step)
+    keep, take, floor = torch.zeros_like(i), torch.zeros_like(i), torch.zeros_like(i)
+    for t in range(tokens):
+        seat = int(seats[t])
+        before = state[seat].clone()
+        now = torch.maximum(f[t] + before, i[t])
+        keep[t], take[t], floor[t] = torch.exp(f[t] + before - now), torch.exp(i[t] - now), torch.exp(-now)
+        state[seat] = now
+    return keep, take, floor
+
+
+def gated_recurrence(q, k, v, decay, write, state, step: StepTensors, heads, key_dim, value_dim, decay_rate, unit_column):
+    tokens = step.num_tokens
+    seats = token_seats(step)
+    width = value_dim - 1 if unit_column else value_dim
+    out = torch.zeros((tokens, heads * value_dim), dtype=torch.float32, device=q.device)
+    decay = whole(decay) if decay is not None else None
+    write = whole(write) if write is not None else None
+    for t in range(tokens):
+        seat = int(seats[t])
+        for head in range(heads):
+            qt = q[t, head * key_dim : (head + 1) * key_dim].float()
+            kt = k[t, head * key_dim : (head + 1) * key_dim].float()
+            vt = v[t, head * width : (head + 1) * width].float()
+            if unit_column:
+                vt = torch.cat([vt, torch.ones(1)])
+            g = decay[t, head] if decay is not None else decay_rate[head].float()
+            u = vt * write[t, head] if write is not None else vt
+            s = g * state[seat, head] + torch.outer(u, kt)
+            state[seat, head] = s
+            out[t, head * value_dim : (head + 1) * value_dim] = s @ qt
+    return out
+
+
+def stabilized_readout(read, floor, heads, value_dim):
+    tokens = read.shape[0]
+    parts = read.float().reshape(tokens, heads, value_dim + 1)
+    lower = torch.maximum(parts[:, :, value_dim].abs(), floor.float())
+    return (parts[:, :, :value_dim] / (lower[:, :, None] + 1e-6)).reshape(tokens, heads * value_dim)
+
+
+def route_top(x, router, top, scoring="sigmoid"):
+    scores = torch.sigmoid(x.float() @ router.float().T)
+    weights, ids = torch.sort(scores, dim=-1, descending=True, stable=True)
+    return ids[:, :top].to(torch.int32).contiguous(), weights[:, :top].contiguous()
+
+
+def routed_swiglu(x, ids, weights, gate_up, down, scale_input=True):
+    tokens, top = ids.shape
+    ff = gate_up.shape[1] // 2
+    out = torch.zeros((top, tokens, x.shape[1]), dtype=torch.float32, device=x.device)
+    for t in range(tokens):
+        for j in range(top):
+            e, w = int(ids[t, j]), weights[t, j].float()
+            z = (x[t].float() * w).to(x.dtype).float() if scale_input else x[t].float()
+            both = gate_up[e].float() @ z
+            hidden = (_silu(both[:ff]) * both[ff:]).to(x.dtype).float()
+            y = down[e].float() @ hidden
+            out[j, t] = y if scale_input else y * w
+    return out
 
 
 def sample(logits, temperatures, uniforms):
@@ -271,8 +394,34 @@ class RefKernels(KernelSet):
     def rope_kv_write(self, qkv, step, kv, rotary, num_heads, num_kv_heads, head_dim, bias=None, q_out=None):
         rope_kv_write(qkv, step, kv, rotary, num_heads, num_kv_heads, head_dim, bias, q_out)
 
-    def attention(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale, chunk=None):
-        out.copy_(attention(qkv, step, kv, num_heads, num_kv_heads, head_dim, window, scale, chunk))
+    def attention(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale, chunk=None, keep_first=0):
+        out.copy_(attention(qkv, step, kv, num_heads, num_kv_heads, head_dim, window, scale, chunk, keep_first))
+
+    def norm_add_rmsnorm(self, delta, delta_weight, delta_eps, residual, weight, eps, out, rows_index=None):
+        new_residual, normed = norm_add_rmsnorm(delta, delta_weight, delta_eps, residual, weight, eps,
+                                                out.dtype if out is not None else self.dtype, rows_index)
+        if rows_index is None and delta is not None:
+            residual.copy_(new_residual)
+        if out is not None:
+            out.copy_(normed)
+
+    def qk_rope_norm_write(self, qk, bias, step, kv, rotary, num_heads, num_kv_heads, head_dim, norm_eps, q_out):
+        q_out.copy_(qk_rope_norm_write(qk, bias, step, kv, rotary, num_heads, num_kv_heads, head_dim, norm_eps, q_out.dtype))
+
+    def activation(self, x, kind="silu", scale=1.0, scaled_columns=0):
+        return activation(x, kind, scale, scaled_columns)
+
+    def exp_gate_scan(self, log_in, log_forget, in_bias, forget_bias, cap, state, step):
+        return exp_gate_scan(log_in, log_forget, in_bias, forget_bias, cap, state, step)
+
+    def stabilized_readout(self, read, floor, heads, value_dim):
+        return stabilized_readout(read, floor, heads, value_dim)
+
+    def route_top(self, x, router, top, scoring="sigmoid"):
+        return route_top(x, router, top, scoring)
+
+    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input=True):
+        return routed_swiglu(x, ids, weights, gate_up, down, scale_input)
 
     def add_layernorm(self, delta, residual, weight, bias, eps, out, rows_index=None):
         new_residual, normed = add_layernorm(delta, residual, weight, bias, eps, self.dtype, rows_index)
@@ -290,12 +439,14 @@ class RefKernels(KernelSet):
         return short_conv(x, weight, bias, state, step, activation)
 
     def linear_recurrence(self, rule, q, k, v, decay, write, state, step, heads, groups, key_dim, value_dim,
-                          decay_rate=None, decay_bias=None, skip=None):
+                          decay_rate=None, decay_bias=None, skip=None, unit_column=False):
+        if rule == "gated":
+            return gated_recurrence(q, k, v, decay, write, state, step, heads, key_dim, value_dim, decay_rate, unit_column)
         return linear_recurrence(rule, q, k, v, decay, write, state, step, heads, groups, key_dim, value_dim,
                                  decay_rate, decay_bias, skip)
 
-    def gated_rmsnorm(self, x, gate, weight, eps, group, gate_first, out):
-        out.copy_(gated_rmsnorm(x, gate, weight, eps, group, gate_first, out.dtype))
+    def gated_rmsnorm(self, x, gate, weight, eps, group, gate_first, out, activation="silu"):
+        out.copy_(gated_rmsnorm(x, gate, weight, eps, group, gate_first, out.dtype, activation))
 
     def sample(self, logits, temperatures, uniforms, out_tokens):
         out_tokens.copy_(sample(logits, temperatures, uniforms))
