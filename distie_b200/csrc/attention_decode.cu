@@ -18,7 +18,8 @@
 //   scratch_o  [tokens, heads, splits, head_dim]   float32
 //   scratch_ml [tokens, heads, splits, 2]          float32 (max, sum)
 //
-// The key range of a token depends only on its position and the window, key_chunk, so the
+// The key range of a token depends only on its position and the window, key_chunk and keep_first (the request's
+// first keys that stay visible beside a window), so the
 // result is the same whatever else the batch holds.  head_dim must be 16, 32, 64,
 // 128 or 256 here; the launcher refuses other sizes and the caller then uses the
 // size-agnostic kernel.
@@ -44,7 +45,7 @@ attention_decode_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict
                         const int* __restrict__ positions, const int* __restrict__ token_seq,
                         const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
                         const T* __restrict__ k_cache, const T* __restrict__ v_cache, int num_heads, int group_size,
-                        int head_chunks, int num_kv_heads, int page_size, int num_pages, int window, int key_chunk, float scale,
+                        int head_chunks, int num_kv_heads, int page_size, int num_pages, int window, int key_chunk, int keep_first, float scale,
                         int* __restrict__ error) {
   constexpr int HEAD_DIM = DL * 8;
   constexpr int ROWS_PER_WARP = 32 / DL;
@@ -88,16 +89,21 @@ attention_decode_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict
     }
   }
 
+  // The request's first `keep_first` keys that the window has moved past are seen all the same: split 0 takes
+  // them ahead of its share of the window.
+  const int kept = split == 0 ? min(keep_first, first) : 0;
+  const int span = kept + (hi >= lo ? hi - lo + 1 : 0);
   // The trip count is the same for every thread of the block: the shuffles below need whole warps.
-  const int iterations = hi >= lo ? (hi - lo + GROUPS * kDecodeUnroll) / (GROUPS * kDecodeUnroll) : 0;
+  const int iterations = (span + GROUPS * kDecodeUnroll - 1) / (GROUPS * kDecodeUnroll);
   for (int it = 0; it < iterations; ++it) {
-    const int base_key = lo + (it * GROUPS + group) * kDecodeUnroll;
+    const int base_index = (it * GROUPS + group) * kDecodeUnroll;
     float kf[kDecodeUnroll][8], vf[kDecodeUnroll][8];
     bool live[kDecodeUnroll];
 #pragma unroll
     for (int u = 0; u < kDecodeUnroll; ++u) {
-      const int key = base_key + u;
-      live[u] = key <= hi;
+      const int index = base_index + u;
+      const int key = index < kept ? index : lo + index - kept;
+      live[u] = index < span;
       int page = 0;
       if (live[u]) {  // a position past the end of the table is reported like a page that is missing
         const int column = key / page_size;
@@ -203,7 +209,7 @@ template <typename T, int DL>
 int launch_decode(const void* q, int q_row_stride, void* out, int out_row_stride, float* scratch_o,
                   float* scratch_ml, const int* positions, const int* token_seq, const int* seq_seat,
                   const int* block_table, int table_width, const void* k_cache, const void* v_cache, int tokens,
-                  int num_heads, int num_kv_heads, int page_size, int num_pages, int window, int key_chunk, float scale,
+                  int num_heads, int num_kv_heads, int page_size, int num_pages, int window, int key_chunk, int keep_first, float scale,
                   int num_splits, int* error, cudaStream_t stream) {
   const int group = num_heads / num_kv_heads;
   // Heads of one kv head are handled GC at a time; pick the chunk that wastes least.
@@ -218,7 +224,7 @@ int launch_decode(const void* q, int q_row_stride, void* out, int out_row_stride
   attention_decode_kernel<T, DL, GCV><<<grid, kDecodeThreads, 0, stream>>>(                                      \
       (const T*)q, q_row_stride, (T*)out, out_row_stride, scratch_o, scratch_ml, positions, token_seq, seq_seat, \
       block_table, table_width, (const T*)k_cache, (const T*)v_cache, num_heads, group, chunks, num_kv_heads,    \
-      page_size, num_pages, window, key_chunk, scale, error)
+      page_size, num_pages, window, key_chunk, keep_first, scale, error)
   switch (gc) {
     case 1: DISTIE_DECODE_CASE(1); break;
     case 2: DISTIE_DECODE_CASE(2); break;
@@ -242,11 +248,11 @@ int dispatch_decode(int head_dim, const void* q, int q_row_stride, void* out, in
                     float* scratch_o, float* scratch_ml, const int* positions, const int* token_seq,
                     const int* seq_seat, const int* block_table, int table_width, const void* k_cache,
                     const void* v_cache, int tokens, int num_heads, int num_kv_heads, int page_size, int num_pages,
-                    int window, int key_chunk, float scale, int num_splits, int* error, cudaStream_t stream) {
+                    int window, int key_chunk, int keep_first, float scale, int num_splits, int* error, cudaStream_t stream) {
 #define DISTIE_DECODE_DIM(DLV)                                                                                   \
   return launch_decode<T, DLV>(q, q_row_stride, out, out_row_stride, scratch_o, scratch_ml, positions, token_seq, \
                                seq_seat, block_table, table_width, k_cache, v_cache, tokens, num_heads,          \
-                               num_kv_heads, page_size, num_pages, window, key_chunk, scale, num_splits, error, stream)
+                               num_kv_heads, page_size, num_pages, window, key_chunk, keep_first, scale, num_splits, error, stream)
   switch (head_dim) {
     case 16: DISTIE_DECODE_DIM(2);
     case 32: DISTIE_DECODE_DIM(4);
@@ -273,22 +279,22 @@ extern "C" int distie_attention_decode(const void* q, int q_row_stride, void* ou
                                        const int* seq_seat, const int* block_table, int table_width,
                                        const void* k_cache, const void* v_cache, int tokens, int num_heads,
                                        int num_kv_heads, int head_dim, int page_size, int num_pages, int window, int key_chunk,
-                                       float scale, int num_splits, int dtype, int* error, cudaStream_t stream) {
+                                       int keep_first, float scale, int num_splits, int dtype, int* error, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
-      num_splits < 1 || num_splits > 65535 || (num_splits > 1 && scratch == nullptr))
+      num_splits < 1 || num_splits > 65535 || (num_splits > 1 && scratch == nullptr) || keep_first < 0)
     return DISTIE_ERR_ARG;
   float* scratch_o = scratch;
   float* scratch_ml = scratch ? scratch + (size_t)tokens * num_heads * num_splits * head_dim : nullptr;
   if (dtype == DISTIE_BF16)
     return dispatch_decode<__nv_bfloat16>(head_dim, q, q_row_stride, out, out_row_stride, scratch_o, scratch_ml,
                                           positions, token_seq, seq_seat, block_table, table_width, k_cache, v_cache,
-                                          tokens, num_heads, num_kv_heads, page_size, num_pages, window, key_chunk, scale,
+                                          tokens, num_heads, num_kv_heads, page_size, num_pages, window, key_chunk, keep_first, scale,
                                           num_splits, error, stream);
   if (dtype == DISTIE_F32)
     return dispatch_decode<float>(head_dim, q, q_row_stride, out, out_row_stride, scratch_o, scratch_ml, positions,
                                   token_seq, seq_seat, block_table, table_width, k_cache, v_cache, tokens, num_heads,
-                                  num_kv_heads, page_size, num_pages, window, key_chunk, scale, num_splits, error, stream);
+                                  num_kv_heads, page_size, num_pages, window, key_chunk, keep_first, scale, num_splits, error, stream);
   return DISTIE_ERR_UNSUPPORTED;
 }
 
@@ -357,5 +363,5 @@ extern "C" int distie_attention_decode_static(const void* q, int q_row_stride, v
   // (max, sum, mix) of every (token, head, split) before the merge kernel reads it.
   return distie_attention_decode(q, q_row_stride, out, out_row_stride, scratch, positions, token_seq, seq_seat,
                                  block_table, table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim,
-                                 page_size, num_pages, window, /*key_chunk=*/0, scale, num_splits, dtype, error, stream);
+                                 page_size, num_pages, window, /*key_chunk=*/0, /*keep_first=*/0, scale, num_splits, dtype, error, stream);
 }

@@ -2,7 +2,8 @@
 //
 // One block per (token, query head).  The token at position `pos` of its request
 // sees the keys `max(0, pos - window + 1) .. pos` of that request (window <= 0:
-// all of them; chunk > 0: only those of its own chunk of that many positions),
+// all of them; chunk > 0: only those of its own chunk of that many positions; keep_first > 0: also the
+// request's first that-many keys when the window has moved past them),
 // which by then are all in the cache: earlier steps stored the older
 // ones and this step's write kernel ran before.  Nothing but the token's position,
 // its request's seat and the block table decides what is read, so the result does
@@ -26,7 +27,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_row_stride, T* __restric
                          const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
                          const T* __restrict__ k_cache, const T* __restrict__ v_cache, int group_size,
                          int num_kv_heads, int head_dim, int value_dim, int page_size, int num_pages, int window,
-                         int chunk, float scale, int* __restrict__ error) {
+                         int chunk, int keep_first, float scale, int* __restrict__ error) {
   __shared__ float sh_m[kGenericWarps], sh_l[kGenericWarps];
   __shared__ float sh_acc[kGenericWarps][kMaxHeadDim];
   const int t = blockIdx.x, head = blockIdx.y;
@@ -36,6 +37,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_row_stride, T* __restric
   const int seat = seq_seat[token_seq[t]];
   const int* table = block_table + (size_t)seat * table_width;
   const int first = first_visible_key(pos, window, chunk);
+  const int kept = min(keep_first, first);  // keys 0 .. kept - 1 lie before the window and are seen all the same
   constexpr int R = kMaxHeadDim / 32;
 
   float qv[R], acc[R];
@@ -47,7 +49,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_row_stride, T* __restric
     acc[i] = 0.f;
   }
   float m = -INFINITY, l = 0.f;
-  for (int key = first + warp; key <= pos; key += kGenericWarps) {
+  for (int index = warp; index < kept + pos - first + 1; index += kGenericWarps) {
+    const int key = index < kept ? index : first + index - kept;
     const int column = key / page_size;
     const int page = column < table_width ? table[column] : -1;
     if (page < 0 || page >= num_pages) {  // a table that does not cover the keys: report, skip
@@ -110,10 +113,11 @@ extern "C" int distie_attention_generic(const void* q, int q_row_stride, void* o
                                         const int* block_table, int table_width, const void* k_cache,
                                         const void* v_cache, int tokens, int num_heads, int num_kv_heads,
                                         int head_dim, int value_dim, int page_size, int num_pages, int window,
-                                        int chunk, float scale, int dtype, int* error, cudaStream_t stream) {
+                                        int chunk, int keep_first, float scale, int dtype, int* error,
+                                        cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || head_dim < 1 ||
-      head_dim > kMaxHeadDim || value_dim < 1 || value_dim > kMaxHeadDim || page_size < 1 || table_width < 1 ||
+      keep_first < 0 || head_dim > kMaxHeadDim || value_dim < 1 || value_dim > kMaxHeadDim || page_size < 1 || table_width < 1 ||
       num_heads > 65535)
     return DISTIE_ERR_ARG;
   const dim3 grid(tokens, num_heads);
@@ -123,12 +127,12 @@ extern "C" int distie_attention_generic(const void* q, int q_row_stride, void* o
     attention_generic_kernel<<<grid, threads, 0, stream>>>(
         (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, positions, token_seq, seq_seat,
         block_table, table_width, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, group, num_kv_heads,
-        head_dim, value_dim, page_size, num_pages, window, chunk, scale, error);
+        head_dim, value_dim, page_size, num_pages, window, chunk, keep_first, scale, error);
   else if (dtype == DISTIE_F32)
     attention_generic_kernel<<<grid, threads, 0, stream>>>(
         (const float*)q, q_row_stride, (float*)out, out_row_stride, positions, token_seq, seq_seat, block_table,
         table_width, (const float*)k_cache, (const float*)v_cache, group, num_kv_heads, head_dim, value_dim, page_size,
-        num_pages, window, chunk, scale, error);
+        num_pages, window, chunk, keep_first, scale, error);
   else
     return DISTIE_ERR_UNSUPPORTED;
   DISTIE_LAUNCH_CHECK();

@@ -42,11 +42,13 @@ NVCC_FLAGS = [
 
 CUDA_UNITS: dict[str, list[str]] = {
     # every model needs these
-    "base": ["elementwise.cu", "attention_generic.cu", "attention_decode.cu", "sampling.cu"],
+    "base": ["elementwise.cu", "normed_residual.cu", "attention_generic.cu", "attention_decode.cu", "sampling.cu"],
     # bfloat16 serving only: tensor-core attention for prompts, weight-streaming products for decoding
     "bf16": ["attention_prefill.cu", "attention_decode_mma.cu", "gemm_tcgen05.cu", "attention_prefill_tcgen05.cu"],
     # models with layer norms, gated heads, short convolutions or linear recurrences (both dtypes)
     "state": ["recurrent.cu"],
+    # models whose feed-forward routes tokens to experts (both dtypes)
+    "routed": ["routed.cu"],
 }
 _HEADERS = ["common.cuh", "tcgen05.cuh", "no_alloc.h"]
 

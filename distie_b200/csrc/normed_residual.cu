@@ -1,0 +1,202 @@
+// Two kernels of layers that norm a sublayer's output before it joins the residual and whose attention
+// keeps a token's key as its value:
+//
+//  * norm_add_rmsnorm: d = sum_j scale_j * term_j (float32); residual += d * rsqrt(mean(d^2) + eps_d) * w_d
+//    (or += d when there is no w_d), written back; out = residual * rsqrt(mean(residual^2) + eps) * w, cast
+//    once at the store.  One block per row; with a list of rows only those are made and the residual stays.
+//  * qk_rope_norm_write: from the float32 projection [q | k] (a matrix or the slices of a split product) plus
+//    bias: the key as projected is stored as the value; q and k are rotated over the first `rotary_dim`
+//    elements of each head (angles pos * inv_freq in float32), then each head is divided by its root mean
+//    square; k goes to its page and q to its buffer.  One block per (token, head).
+//
+// All arithmetic is float32; T is the type of what is stored for the next product or in the cache.
+#include "common.cuh"
+
+namespace distie {
+
+constexpr int kResidualTerms = 24;
+struct ResidualTerms {
+  const float* ptr[kResidualTerms];
+  float scale[kResidualTerms];
+  int count;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+norm_add_rmsnorm_kernel(ResidualTerms terms, const float* __restrict__ delta_weight, float delta_eps,
+                        float* __restrict__ residual, const float* __restrict__ weight, float eps, T* __restrict__ out,
+                        const int* __restrict__ rows_index, int hidden) {
+  extern __shared__ __align__(16) float row_s[];  // the summed terms, then the new residual
+  __shared__ float scratch[32];
+  const int i = blockIdx.x;
+  const size_t row = rows_index ? (size_t)rows_index[i] : (size_t)i;
+  float* res = residual + row * hidden;
+  float ss = 0.f;
+  if (terms.count > 0) {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      float d = 0.f;
+      for (int j = 0; j < terms.count; ++j) d += terms.scale[j] * terms.ptr[j][row * hidden + c];
+      row_s[c] = d;
+      ss += d * d;
+    }
+    float factor = 1.f;
+    if (delta_weight) factor = rsqrtf(block_sum(ss, scratch) / (float)hidden + delta_eps);
+    ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float r = res[c] + (delta_weight ? row_s[c] * factor * delta_weight[c] : row_s[c]);
+      row_s[c] = r;
+      if (!rows_index) res[c] = r;
+      ss += r * r;
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float r = res[c];
+      row_s[c] = r;
+      ss += r * r;
+    }
+  }
+  if (!out) return;
+  const float unit = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+  T* out_row = out + (size_t)i * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) out_row[c] = from_float<T>(row_s[c] * unit * weight[c]);
+}
+
+struct SlicedRows {
+  const float* p;
+  int stride;
+  int splits;
+  long long split_stride;
+  __device__ __forceinline__ float at(size_t row, int col) const {
+    const float* q = p + row * stride + col;
+    float v = q[0];
+    for (int s = 1; s < splits; ++s) v += q[(size_t)s * split_stride];
+    return v;
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_rope_norm_write_kernel(SlicedRows qk, const float* __restrict__ bias, T* __restrict__ q_out, int q_out_stride,
+                          const int* __restrict__ positions, const int* __restrict__ token_seq,
+                          const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
+                          const float* __restrict__ inv_freq, float factor, T* __restrict__ k_cache,
+                          T* __restrict__ v_cache, int num_heads, int num_kv_heads, int head_dim, int rotary_dim,
+                          int interleaved, int page_size, int num_pages, int write, int normed, float norm_eps,
+                          int* __restrict__ error) {
+  extern __shared__ __align__(16) float head_s[];  // head_dim floats: the head as projected, then rotated
+  __shared__ float scratch[32];
+  const int t = blockIdx.x, head = blockIdx.y;
+  const bool is_key = head >= num_heads;
+  if (is_key && !write) return;
+  const int pos = positions[t];
+  const int column0 = head * head_dim;
+  for (int e = threadIdx.x; e < head_dim; e += blockDim.x)
+    head_s[e] = qk.at(t, column0 + e) + (bias ? bias[column0 + e] : 0.f);
+  __syncthreads();
+  size_t cache_row = 0;
+  bool store = !is_key;
+  if (is_key) {
+    const int seat = seq_seat[token_seq[t]];
+    const int column = pos / page_size;
+    const int page = column < table_width ? block_table[(size_t)seat * table_width + column] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0 && error) atomicExch(error, 2);
+    } else {
+      store = true;
+      cache_row = (((size_t)page * num_kv_heads + (head - num_heads)) * page_size + pos % page_size) * head_dim;
+      for (int e = threadIdx.x; e < head_dim; e += blockDim.x) v_cache[cache_row + e] = from_float<T>(head_s[e]);
+    }
+  }
+  // Rotation: every pair is read and written by one thread.
+  const int half = rotary_dim / 2;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+    float sn, cs;
+    sincosf((float)pos * inv_freq[i], &sn, &cs);
+    sn *= factor;
+    cs *= factor;
+    const float u = head_s[a], v = head_s[b];
+    const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+    head_s[a] = ru;
+    head_s[b] = rv;
+    ss += ru * ru + rv * rv;
+  }
+  for (int e = rotary_dim + threadIdx.x; e < head_dim; e += blockDim.x) ss += head_s[e] * head_s[e];
+  float unit = 1.f;
+  if (normed) unit = rsqrtf(block_sum(ss, scratch) / (float)head_dim + norm_eps);
+  else __syncthreads();
+  if (!store) return;
+  T* dst = is_key ? k_cache + cache_row : q_out + (size_t)t * q_out_stride + column0;
+  for (int e = threadIdx.x; e < head_dim; e += blockDim.x) dst[e] = from_float<T>(head_s[e] * unit);
+}
+
+}  // namespace distie
+
+using namespace distie;
+
+// terms: `num_terms` float32 matrices [rows of the residual, hidden] with a scale each (none: nothing is added).
+// delta_weight null: the sum joins the residual as it is.  out null: only the residual is moved on.
+extern "C" int distie_norm_add_rmsnorm(const float* const* term_ptrs, const float* term_scales, int num_terms,
+                                       const float* delta_weight, float delta_eps, float* residual, const float* weight,
+                                       float eps, void* out, const int* rows_index, int rows, int hidden, int dtype,
+                                       cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hidden < 1 || num_terms < 0 || num_terms > kResidualTerms || residual == nullptr || (out && !weight))
+    return DISTIE_ERR_ARG;
+  ResidualTerms terms;
+  terms.count = num_terms;
+  for (int j = 0; j < num_terms; ++j) { terms.ptr[j] = term_ptrs[j]; terms.scale[j] = term_scales[j]; }
+  const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+  const size_t shared = (size_t)hidden * sizeof(float);
+  if (shared > 200 * 1024) return DISTIE_ERR_UNSUPPORTED;
+  if (dtype == DISTIE_BF16) {
+    if (shared > 48 * 1024)
+      cudaFuncSetAttribute(norm_add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    norm_add_rmsnorm_kernel<<<rows, threads, shared, stream>>>(terms, delta_weight, delta_eps, residual, weight, eps,
+                                                               (__nv_bfloat16*)out, rows_index, hidden);
+  } else if (dtype == DISTIE_F32) {
+    if (shared > 48 * 1024)
+      cudaFuncSetAttribute(norm_add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    norm_add_rmsnorm_kernel<<<rows, threads, shared, stream>>>(terms, delta_weight, delta_eps, residual, weight, eps,
+                                                               (float*)out, rows_index, hidden);
+  } else {
+    return DISTIE_ERR_UNSUPPORTED;
+  }
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+// qk: float32 [tokens, (heads + kv_heads) * head_dim] with row stride `qk_stride`, or `splits` such matrices
+// `split_stride` floats apart whose sum it is.  write == 0: only q is made.  normed == 0: no division.
+extern "C" int distie_qk_rope_norm_write(const float* qk, int qk_stride, int splits, long long split_stride,
+                                         const float* bias, void* q_out, int q_out_stride, const int* positions,
+                                         const int* token_seq, const int* seq_seat, const int* block_table,
+                                         int table_width, const float* inv_freq, float factor, void* k_cache,
+                                         void* v_cache, int tokens, int num_heads, int num_kv_heads, int head_dim,
+                                         int rotary_dim, int interleaved, int page_size, int num_pages, int write,
+                                         int normed, float norm_eps, int dtype, int* error, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (num_heads < 1 || num_kv_heads < 1 || head_dim < 1 || head_dim > 1024 || rotary_dim < 0 || rotary_dim > head_dim ||
+      (rotary_dim & 1) || (rotary_dim > 0 && inv_freq == nullptr) || splits < 1 || page_size < 1 ||
+      num_heads + num_kv_heads > 65535 || (write && (k_cache == nullptr || v_cache == nullptr)))
+    return DISTIE_ERR_ARG;
+  const dim3 grid(tokens, num_heads + num_kv_heads);
+  const int threads = head_dim >= 256 ? 256 : (head_dim >= 128 ? 128 : 64);
+  const size_t shared = (size_t)head_dim * sizeof(float);
+  const SlicedRows rows{qk, qk_stride, splits, split_stride};
+  if (dtype == DISTIE_BF16)
+    qk_rope_norm_write_kernel<<<grid, threads, shared, stream>>>(
+        rows, bias, (__nv_bfloat16*)q_out, q_out_stride, positions, token_seq, seq_seat, block_table, table_width,
+        inv_freq, factor, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_heads, num_kv_heads, head_dim,
+        rotary_dim, interleaved, page_size, num_pages, write, normed, norm_eps, error);
+  else if (dtype == DISTIE_F32)
+    qk_rope_norm_write_kernel<<<grid, threads, shared, stream>>>(
+        rows, bias, (float*)q_out, q_out_stride, positions, token_seq, seq_seat, block_table, table_width, inv_freq,
+        factor, (float*)k_cache, (float*)v_cache, num_heads, num_kv_heads, head_dim, rotary_dim, interleaved, page_size,
+        num_pages, write, normed, norm_eps, error);
+  else
+    return DISTIE_ERR_UNSUPPORTED;
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}

@@ -1,7 +1,9 @@
 // Kernels of layers that keep a state per request instead of (or beside) a cache of keys:
 // the residual sum + LayerNorm over a weighted sum of terms, the paged key/value write of
 // layers that rotate nothing, the sigmoid gate per head, the short causal convolution,
-// the linear recurrence (gated delta rule and state-space duality) and the gated RMS norm.
+// the linear recurrence (gated delta rule, state-space duality, and plainly gated with an optional
+// normaliser column), the gated RMS norm, and what a memory with exponential gates needs around its
+// recurrence: an activation over a split product, the gates' scan under a running maximum, the stabilised read-out.
 //
 // Conventions.  Everything between a layer's projections and its output projection is
 // float32 here: inputs are float32 matrices with a row stride (views into a projection's
@@ -19,6 +21,7 @@ namespace distie {
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return log1pf(expf(-fabsf(z))) + fmaxf(z, 0.f); }
+__device__ __forceinline__ float gate_f(int sigmoid, float z) { return sigmoid ? sigmoid_f(z) : silu_f(z); }
 
 // A float32 matrix that may still be the slices of a split product: `splits` matrices `split_stride` floats apart
 // whose sum it is (splits == 1: the matrix itself).  Loads add the slices up, in their order.
@@ -401,7 +404,10 @@ __global__ void short_conv_state_kernel(Sliced x, float* __restrict__ state,
 // instead of one after the other.  Tokens come in tiles of 16 that cp.async brings into shared memory a tile
 // ahead of the walk.
 // ---------------------------------------------------------------------------
-constexpr int kRuleDelta = 0, kRuleSsd = 1;
+//   kGated: nothing is normalised; g = decay[t, h] as given (or the constant rate[h] when there is no decay);
+//           u = write[t, h] v (or v when there is no write).  With a unit column (v_dim = value_dim - 1) the
+//           last column of every head's state sees the value 1 for every token: it carries n <- g n + write k.
+constexpr int kRuleDelta = 0, kRuleSsd = 1, kRuleGated = 2;
 constexpr int kScanThreads = 64, kScanTile = 16;
 
 struct ScanArgs {
@@ -416,6 +422,7 @@ struct ScanArgs {
   int out_stride;
   const int *seq_bounds, *seq_seat;
   int tokens, heads, groups, key_dim, value_dim;
+  int v_dim;  // elements of v per head: value_dim, or value_dim - 1 when the state's last column is the unit column
   float* scalars;  // [tokens, heads, 2]: g and the factor of u
   float* kq;       // [tokens, groups]: k . q
 };
@@ -424,9 +431,16 @@ template <int RULE>
 __global__ void __launch_bounds__(128) recurrence_prepare_kernel(ScanArgs a) {
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int h = threadIdx.x; h < a.heads; h += blockDim.x) {
+    float g, factor;
+    if (RULE == kRuleGated) {
+      g = a.decay ? Sliced{a.decay, a.decay_stride, a.splits, a.split_stride}.at(t, h) : a.rate[h];
+      factor = a.write ? Sliced{a.write, a.write_stride, a.splits, a.split_stride}.at(t, h) : 1.f;
+      a.scalars[((size_t)t * a.heads + h) * 2] = g;
+      a.scalars[((size_t)t * a.heads + h) * 2 + 1] = factor;
+      continue;
+    }
     const float rate = expf(a.rate[h]), bias = a.bias ? a.bias[h] : 0.f;
     const float w = Sliced{a.write, a.write_stride, a.splits, a.split_stride}.at(t, h);
-    float g, factor;
     if (RULE == kRuleDelta) {
       g = expf(-rate * softplus_f(Sliced{a.decay, a.decay_stride, a.splits, a.split_stride}.at(t, h) + bias));
       factor = sigmoid_f(w);
@@ -520,8 +534,8 @@ __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArg
     }
     for (int idx = tid; idx < count * kScanColumns; idx += kScanThreads) {
       const int tok = idx / kScanColumns, c = idx % kScanColumns, cj = blockIdx.z * kScanColumns + c;
-      const bool live = cj < a.value_dim;
-      cp_async_f1(&st.v[tok][c], a.v + (size_t)(tile + (live ? tok : 0)) * a.v_stride + head * a.value_dim + (live ? cj : 0), live);
+      const bool live = cj < a.v_dim;  // (the unit column has no element of v: the walk puts 1 in its place)
+      cp_async_f1(&st.v[tok][c], a.v + (size_t)(tile + (live ? tok : 0)) * a.v_stride + head * a.v_dim + (live ? cj : 0), live);
     }
     if (tid < count) {
       const bool live = true;
@@ -544,6 +558,7 @@ __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArg
       S[4 * r + c] = (valid && i < a.key_dim) ? column[i] : 0.f;
     }
   const float skip = (RULE == kRuleSsd && a.skip) ? a.skip[head] : 0.f;
+  const bool unit_column = RULE == kRuleGated && j >= a.v_dim;
 
   int buffer = 0;
   for (int tile = first; tile < end; tile += kScanTile, buffer ^= 1) {
@@ -565,7 +580,8 @@ __global__ void __launch_bounds__(kScanThreads) linear_recurrence_kernel(ScanArg
         qq[4 * r] = qv.x; qq[4 * r + 1] = qv.y; qq[4 * r + 2] = qv.z; qq[4 * r + 3] = qv.w;
       }
       const float4 per_token = *reinterpret_cast<const float4*>(st.scalars[tok]);
-      const float g = per_token.x, factor = per_token.y, kq = per_token.z, vj = st.v[tok][col_local];
+      const float g = per_token.x, factor = per_token.y, kq = per_token.z;
+      const float vj = unit_column ? 1.f : st.v[tok][col_local];
       // S^T k and S^T q of this column before the write, four partial sums each
       float dk[4] = {0.f, 0.f, 0.f, 0.f}, dq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -642,7 +658,8 @@ static cudaError_t launch_scan(const ScanArgs& a, int num_seqs, cudaStream_t str
 
 // ---------------------------------------------------------------------------
 // RMS norm over groups of `group` neighbouring columns with a SiLU gate, a warp per (token, group):
-//   gate_first: norm(x * silu(gate)) * weight;   else: norm(x) * weight * silu(gate).
+//   gate_first (bit 0 of the mode): norm(x * silu(gate)) * weight;   else: norm(x) * weight * silu(gate).
+//   bit 1 of the mode: sigmoid(gate) stands where silu(gate) does.
 // weight has `weight_len` elements and repeats along the row.
 // ---------------------------------------------------------------------------
 template <typename T>
@@ -650,19 +667,21 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ x, int x_stride, 
                                      const float* __restrict__ weight, int weight_len, T* __restrict__ out,
                                      int out_stride, int tokens, int groups, int group, float eps, int gate_first) {
   const int lane = threadIdx.x & 31;
+  const int gate_sigmoid = gate_first >> 1;  // bit 1 of the mode: the gate is sigmoid(gate) instead of silu(gate)
+  gate_first &= 1;
   const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= (long long)tokens * groups) return;
   const int t = (int)(unit / groups), part = (int)(unit % groups);
   const float* xr = x + (size_t)t * x_stride + (size_t)part * group;
   float sq = 0.f;
   for (int i = lane; i < group; i += 32) {
-    const float v = gate_first ? xr[i] * silu_f(gate.at(t, part * group + i)) : xr[i];
+    const float v = gate_first ? xr[i] * gate_f(gate_sigmoid, gate.at(t, part * group + i)) : xr[i];
     sq += v * v;
   }
   const float inv = 1.f / sqrtf(warp_sum(sq) / (float)group + eps);
   T* dst = out + (size_t)t * out_stride + (size_t)part * group;
   for (int i = lane; i < group; i += 32) {
-    const float s = silu_f(gate.at(t, part * group + i));
+    const float s = gate_f(gate_sigmoid, gate.at(t, part * group + i));
     const float w = weight[(part * group + i) % weight_len];
     dst[i] = from_float<T>(gate_first ? xr[i] * s * inv * w : xr[i] * inv * w * s);
   }
@@ -677,6 +696,8 @@ gated_rmsnorm_vec_kernel(const float* __restrict__ x, int x_stride, Sliced gate,
                          int weight_len, T* __restrict__ out, int out_stride, int tokens, int groups, int group,
                          float eps, int gate_first) {
   __shared__ float scratch[32];
+  const int gate_sigmoid = gate_first >> 1;
+  gate_first &= 1;
   const int lane = threadIdx.x % LANES;
   const long long unit = LANES == 32 ? (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5) : blockIdx.x;
   const bool live = unit < (long long)tokens * groups;  // (a block is either wholly live or a warp per unit)
@@ -691,7 +712,7 @@ gated_rmsnorm_vec_kernel(const float* __restrict__ x, int x_stride, Sliced gate,
     if (i < group) {
       v[p] = *reinterpret_cast<const float4*>(xr + i);
       const float4 g = gate.at4(t, part * group + i);
-      s[p] = make_float4(silu_f(g.x), silu_f(g.y), silu_f(g.z), silu_f(g.w));
+      s[p] = make_float4(gate_f(gate_sigmoid, g.x), gate_f(gate_sigmoid, g.y), gate_f(gate_sigmoid, g.z), gate_f(gate_sigmoid, g.w));
       if (gate_first) v[p] = make_float4(v[p].x * s[p].x, v[p].y * s[p].y, v[p].z * s[p].z, v[p].w * s[p].w);
       sq += (v[p].x * v[p].x + v[p].y * v[p].y) + (v[p].z * v[p].z + v[p].w * v[p].w);
     }
@@ -709,6 +730,83 @@ gated_rmsnorm_vec_kernel(const float* __restrict__ x, int x_stride, Sliced gate,
       if (!gate_first) o = make_float4(o.x * s[p].x, o.y * s[p].y, o.z * s[p].z, o.w * s[p].w);
       store4(dst + i, o);
     }
+  }
+}
+
+
+// ---------------------------------------------------------------------------
+// out[t, c] = act(x[t, c]) (* scale for c < scaled_columns), x a matrix or the slices of a split product.
+// ---------------------------------------------------------------------------
+__global__ void activation_kernel(Sliced x, float* __restrict__ out, int tokens, int columns, int silu, float scale,
+                                  int scaled_columns) {
+  const size_t total = (size_t)tokens * columns;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / columns;
+    const int c = (int)(idx % columns);
+    float v = x.at(t, c);
+    if (silu) v = silu_f(v);
+    if (c < scaled_columns) v *= scale;
+    out[idx] = v;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Exponential gates under a running maximum, one block per request of the step:
+//   i = cap tanh((x_i + b_i) / cap);  f = logsigmoid(cap tanh((x_f + b_f) / cap));  m_t = max(f_t + m_(t-1), i_t)
+//   keep = exp(f + m_(t-1) - m_t);  take = exp(i - m_t);  floor = exp(-m_t);  m lives in state[seat, head].
+// Three passes: the gates of all tokens side by side, the maximum token by token (a thread per head: two additions
+// and a maximum per token on the chain), the exponentials side by side again.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+exp_gate_scan_kernel(Sliced log_in, Sliced log_forget, const float* __restrict__ in_bias,
+                     const float* __restrict__ forget_bias, float cap, float* __restrict__ state,
+                     const int* __restrict__ seq_bounds, const int* __restrict__ seq_seat, int heads,
+                     float* __restrict__ keep, float* __restrict__ take, float* __restrict__ floor_out) {
+  const int row = blockIdx.x;
+  const int first = seq_bounds[row], end = seq_bounds[row + 1];
+  const int count = (end - first) * heads;
+  for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
+    const int t = first + idx / heads, h = idx % heads;
+    const float i = cap * tanhf((log_in.at(t, h) + in_bias[h]) / cap);
+    const float z = cap * tanhf((log_forget.at(t, h) + forget_bias[h]) / cap);
+    take[(size_t)t * heads + h] = i;
+    keep[(size_t)t * heads + h] = -softplus_f(-z);
+  }
+  __syncthreads();
+  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+    float* slot = state + (size_t)seq_seat[row] * heads + h;
+    float m = *slot;
+    for (int t = first; t < end; ++t) {
+      const size_t at = (size_t)t * heads + h;
+      const float f = keep[at], i = take[at];
+      const float m_new = fmaxf(f + m, i);
+      keep[at] = f + m - m_new;
+      take[at] = i - m_new;
+      floor_out[at] = -m_new;
+      m = m_new;
+    }
+    *slot = m;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
+    const size_t at = (size_t)first * heads + idx;
+    keep[at] = expf(keep[at]);
+    take[at] = expf(take[at]);
+    floor_out[at] = expf(floor_out[at]);
+  }
+}
+
+// out[t, h, c] = read[t, h, c] / (max(|read[t, h, value_dim]|, floor[t, h]) + 1e-6) for c < value_dim.
+__global__ void stabilized_readout_kernel(const float* __restrict__ read, int read_stride, const float* __restrict__ floor_in,
+                                          float* __restrict__ out, int tokens, int heads, int value_dim) {
+  const size_t total = (size_t)tokens * heads * value_dim;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(idx % value_dim);
+    const size_t th = idx / value_dim;
+    const size_t t = th / heads;
+    const int h = (int)(th % heads);
+    const float* row = read + t * read_stride + (size_t)h * (value_dim + 1);
+    out[idx] = row[c] / (fmaxf(fabsf(row[value_dim]), floor_in[th]) + 1e-6f);
   }
 }
 
@@ -866,6 +964,8 @@ extern "C" int distie_short_conv(const float* x_ptr, int x_stride, int splits, l
   return 0;
 }
 
+// rule 2 (gated): decay may be null (rate[h] is then the decay itself) and write may be null (1); with `unit_column`
+// v has value_dim - 1 elements per head and the state's last column per head is fed the value 1.
 // q and k are overwritten by their unit vectors under the delta rule.  scratch: tokens * (2 heads + groups) floats.
 // decay and write may be slices of a split product (`splits` of them, `split_stride` floats apart).
 extern "C" int distie_linear_recurrence(int rule, float* q, int q_stride, float* k, int k_stride,
@@ -875,12 +975,14 @@ extern "C" int distie_linear_recurrence(int rule, float* q, int q_stride, float*
                                         const float* skip, float* state, float* out, int out_stride,
                                         float* scratch, const int* seq_bounds, const int* seq_seat, int tokens,
                                         int num_seqs, int heads, int groups, int key_dim, int value_dim,
-                                        cudaStream_t stream) {
+                                        int unit_column, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (heads < 1 || groups < 1 || heads % groups || key_dim < 1 || value_dim < 1 || num_seqs < 1 || heads > 65535)
     return DISTIE_ERR_ARG;
   if (key_dim > 256 || (value_dim + 1) / 2 > 65535) return DISTIE_ERR_UNSUPPORTED;
-  if (rate == nullptr || state == nullptr || scratch == nullptr || (rule == kRuleDelta && decay == nullptr))
+  if (state == nullptr || scratch == nullptr || (rule == kRuleDelta && decay == nullptr) ||
+      (rule != kRuleGated && (rate == nullptr || write == nullptr || unit_column)) ||
+      (rule == kRuleGated && rate == nullptr && decay == nullptr) || (unit_column && value_dim < 2))
     return DISTIE_ERR_ARG;
   ScanArgs a;
   a.q = q; a.k = k; a.v = v; a.decay = decay; a.write = write;
@@ -890,11 +992,13 @@ extern "C" int distie_linear_recurrence(int rule, float* q, int q_stride, float*
   a.rate = rate; a.bias = bias; a.skip = skip; a.state = state; a.out = out; a.out_stride = out_stride;
   a.seq_bounds = seq_bounds; a.seq_seat = seq_seat;
   a.tokens = tokens; a.heads = heads; a.groups = groups; a.key_dim = key_dim; a.value_dim = value_dim;
+  a.v_dim = unit_column ? value_dim - 1 : value_dim;
   a.scalars = scratch;
   a.kq = scratch + (size_t)tokens * heads * 2;
   cudaError_t err;
   if (rule == kRuleDelta) err = launch_scan<kRuleDelta>(a, num_seqs, stream);
   else if (rule == kRuleSsd) err = launch_scan<kRuleSsd>(a, num_seqs, stream);
+  else if (rule == kRuleGated) err = launch_scan<kRuleGated>(a, num_seqs, stream);
   else return DISTIE_ERR_ARG;
   return err == cudaSuccess ? 0 : (int)err;
 }
@@ -934,6 +1038,46 @@ extern "C" int distie_gated_rmsnorm(const float* x, int x_stride, const float* g
   if (dtype == DISTIE_BF16) DISTIE_GATED(__nv_bfloat16);
   else DISTIE_GATED(float);
 #undef DISTIE_GATED
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int distie_activation(const float* x, int x_stride, int splits, long long split_stride, float* out, int tokens,
+                                 int columns, int silu, float scale, int scaled_columns, cudaStream_t stream) {
+  if (tokens <= 0 || columns <= 0) return 0;
+  if (splits < 1 || scaled_columns < 0 || scaled_columns > columns) return DISTIE_ERR_ARG;
+  const size_t total = (size_t)tokens * columns;
+  const unsigned blocks = (unsigned)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  activation_kernel<<<blocks, 256, 0, stream>>>(Sliced{x, x_stride, splits, split_stride}, out, tokens, columns, silu,
+                                               scale, scaled_columns);
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+// log_in and log_forget [tokens, heads] (views of one projection: the same slices); keep, take, floor [tokens, heads]
+// contiguous; state [seats, heads].
+extern "C" int distie_exp_gate_scan(const float* log_in, const float* log_forget, int gate_stride, int splits,
+                                    long long split_stride, const float* in_bias, const float* forget_bias, float cap,
+                                    float* state, const int* seq_bounds, const int* seq_seat, int num_seqs, int heads,
+                                    float* keep, float* take, float* floor_out, cudaStream_t stream) {
+  if (num_seqs <= 0) return 0;
+  if (heads < 1 || splits < 1 || !(cap > 0.f) || state == nullptr || in_bias == nullptr || forget_bias == nullptr)
+    return DISTIE_ERR_ARG;
+  exp_gate_scan_kernel<<<num_seqs, 256, 0, stream>>>(Sliced{log_in, gate_stride, splits, split_stride},
+                                                     Sliced{log_forget, gate_stride, splits, split_stride}, in_bias,
+                                                     forget_bias, cap, state, seq_bounds, seq_seat, heads, keep, take,
+                                                     floor_out);
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int distie_stabilized_readout(const float* read, int read_stride, const float* floor_in, float* out, int tokens,
+                                         int heads, int value_dim, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (heads < 1 || value_dim < 1) return DISTIE_ERR_ARG;
+  const size_t total = (size_t)tokens * heads * value_dim;
+  const unsigned blocks = (unsigned)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  stabilized_readout_kernel<<<blocks, 256, 0, stream>>>(read, read_stride, floor_in, out, tokens, heads, value_dim);
   DISTIE_LAUNCH_CHECK();
   return 0;
 }

@@ -1,0 +1,412 @@
+// Kernels of a routed feed-forward: every token goes through `top` of `experts` small SwiGLU layers.
+//
+//   route_top     logits = x W_router^T in float32, scores = sigmoid(logits), the `top` largest per token
+//                 (ties to the lower index) with their scores.  One block per token.
+//   route_plan    (token, choice) pairs sorted by expert: for every slot of the sorted order the token it reads,
+//                 the weight of the pair and the row of the output it writes; the list of row tiles (expert,
+//                 first slot, rows) that the grouped products walk.  One block.
+//   grouped products over the sorted slots, a tile of rows of one expert per block:
+//                 hidden = silu(z Wg_e^T) * (z Wu_e^T) with z = weight * x[token] (or x[token]);
+//                 out[choice, token, :] = hidden Wd_e^T (times the weight when it was not on the input).
+//
+// Nothing reads host-side batch data: counts, offsets and tiles stay on the device, so a captured decode step
+// replays these kernels for whatever tokens it is given.  A row's result depends on its own token and expert
+// only (the order of accumulation over K is fixed), never on what else was routed to the expert.
+// Accumulation is float32; T (float or bfloat16) is the type of activations and weights.
+#include "common.cuh"
+
+#include <mma.h>
+
+namespace distie {
+
+__device__ __forceinline__ float routed_silu(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float routed_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
+
+constexpr int kRouteThreads = 128;
+constexpr int kMaxTop = 32;
+
+// scores_s: `experts` floats of dynamic shared memory.
+template <typename T>
+__global__ void __launch_bounds__(kRouteThreads)
+route_top_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ router, int hidden, int experts, int top,
+                 int* __restrict__ ids, float* __restrict__ weights) {
+  extern __shared__ float scores_s[];
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const T* row = x + (size_t)t * x_stride;
+  for (int e = warp; e < experts; e += kRouteThreads / 32) {
+    const T* w = router + (size_t)e * hidden;
+    float dot = 0.f;
+    for (int i = lane; i < hidden; i += 32) dot += to_float(row[i]) * to_float(w[i]);
+    dot = warp_sum(dot);
+    if (lane == 0) scores_s[e] = routed_sigmoid(dot);
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  for (int j = 0; j < top; ++j) {
+    float best = -1.f;  // scores lie in [0, 1]; a score taken is set to -2
+    int at = experts;
+    for (int e = lane; e < experts; e += 32) {
+      const float s = scores_s[e];
+      if (s > best) { best = s; at = e; }  // the first of equal scores within a lane: the lower index
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+      const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
+      if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
+    }
+    if (lane == 0) {
+      ids[(size_t)t * top + j] = at;
+      weights[(size_t)t * top + j] = best;
+      scores_s[at] = -2.f;
+    }
+    __syncwarp();
+  }
+}
+
+// plan layout (int32): [0] number of tiles; [1 .. 1 + experts] offsets of the experts' slots; then
+// tile_expert[max_tiles], tile_first[max_tiles], tile_rows[max_tiles]; then per slot source[pairs], dest[pairs];
+// scale[pairs] (float bits).  max_tiles = pairs / tile + experts (rounded up).
+struct RoutePlan {
+  int* num_tiles;
+  int* offsets;
+  int* tile_expert;
+  int* tile_first;
+  int* tile_rows;
+  int* source;
+  int* dest;
+  float* scale;
+};
+
+__host__ __device__ inline RoutePlan plan_views(int* base, int pairs, int experts, int tile) {
+  const int max_tiles = (pairs + tile - 1) / tile + experts;
+  RoutePlan p;
+  p.num_tiles = base;
+  p.offsets = base + 1;
+  p.tile_expert = p.offsets + experts + 1;
+  p.tile_first = p.tile_expert + max_tiles;
+  p.tile_rows = p.tile_first + max_tiles;
+  p.source = p.tile_rows + max_tiles;
+  p.dest = p.source + pairs;
+  p.scale = reinterpret_cast<float*>(p.dest + pairs);
+  return p;
+}
+
+// counts_s: 2 * experts ints of dynamic shared memory (counts, then cursors).
+__global__ void __launch_bounds__(1024)
+route_plan_kernel(const int* __restrict__ ids, const float* __restrict__ weights, int tokens, int top, int experts,
+                  int tile, int* __restrict__ plan_base, int* __restrict__ error) {
+  extern __shared__ int counts_s[];
+  int* cursor_s = counts_s + experts;
+  const int pairs = tokens * top;
+  const RoutePlan plan = plan_views(plan_base, pairs, experts, tile);
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts_s[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e < 0 || e >= experts) { if (error) atomicExch(error, 7); continue; }
+    atomicAdd(&counts_s[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      const int count = counts_s[e];
+      plan.offsets[e] = at;
+      cursor_s[e] = at;
+      for (int first = 0; first < count; first += tile) {
+        plan.tile_expert[tiles] = e;
+        plan.tile_first[tiles] = at + first;
+        plan.tile_rows[tiles] = min(tile, count - first);
+        ++tiles;
+      }
+      at += count;
+    }
+    plan.offsets[experts] = at;
+    *plan.num_tiles = tiles;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e < 0 || e >= experts) continue;
+    const int slot = atomicAdd(&cursor_s[e], 1);
+    const int token = p / top, choice = p % top;
+    plan.source[slot] = token;
+    plan.dest[slot] = choice * tokens + token;
+    plan.scale[slot] = weights[p];
+  }
+}
+
+// ---- grouped products, float32 arithmetic on the FMA pipe ---------------------------------------------------------
+constexpr int kTileM = 32, kTileN = 64, kTileK = 16, kGroupedThreads = 256;
+
+// C[slot, n] = sum_k A[row(slot), k] * W[e][n, k] for the slots of one tile of one expert.
+//   SWIGLU: W is [experts, 2 N, K]; C = silu(A Wg^T) * (A Wu^T), stored as T in `out` [pairs, N] by slot.
+//   else:   W is [experts, N, K]; C stored as float32 in `out32` at row dest[slot] (times scale[slot] with scale_out).
+// `gather`: A's row of a slot is source[slot] and is multiplied by scale[slot] when scale_in is set; otherwise the
+// slot's own row.
+template <typename T, bool SWIGLU>
+__global__ void __launch_bounds__(kGroupedThreads)
+grouped_product_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ w, int* __restrict__ plan_base,
+                       int pairs, int experts, T* __restrict__ out, float* __restrict__ out32, int N, int K, int gather,
+                       int scale_in, int scale_out) {
+  const RoutePlan plan = plan_views(plan_base, pairs, experts, kTileM);
+  const int tile = blockIdx.x;
+  if (tile >= *plan.num_tiles) return;
+  const int expert = plan.tile_expert[tile], first = plan.tile_first[tile], rows = plan.tile_rows[tile];
+  const int n0 = blockIdx.y * kTileN;
+  __shared__ float a_s[kTileK][kTileM + 1];
+  __shared__ float w_s[SWIGLU ? 2 : 1][kTileK][kTileN + 1];
+  __shared__ int src_s[kTileM];
+  __shared__ float scale_s[kTileM];
+  const int tid = threadIdx.x;
+  if (tid < kTileM) {
+    const int slot = first + min(tid, rows - 1);
+    src_s[tid] = gather ? plan.source[slot] : slot;
+    scale_s[tid] = plan.scale[slot];
+  }
+  __syncthreads();
+  const int ty = tid / 16, tx = tid % 16;  // rows 2 ty, 2 ty + 1; columns 4 tx .. 4 tx + 3
+  float acc[2][4] = {}, acc_up[2][4] = {};
+  const size_t w_rows = SWIGLU ? 2 * (size_t)N : (size_t)N;
+  const T* w_e = w + (size_t)expert * w_rows * K;
+  for (int k0 = 0; k0 < K; k0 += kTileK) {
+    for (int idx = tid; idx < kTileM * kTileK; idx += kGroupedThreads) {
+      const int r = idx / kTileK, kk = idx % kTileK;
+      float v = 0.f;
+      if (r < rows && k0 + kk < K) {
+        v = to_float(a[(size_t)src_s[r] * a_stride + k0 + kk]);
+        if (scale_in) v = to_float(from_float<T>(v * scale_s[r]));  // the expert reads weight * x in the engine's type
+      }
+      a_s[kk][r] = v;
+    }
+    for (int idx = tid; idx < kTileN * kTileK; idx += kGroupedThreads) {
+      const int n = idx / kTileK, kk = idx % kTileK;
+      const bool live = n0 + n < N && k0 + kk < K;
+      w_s[0][kk][n] = live ? to_float(w_e[(size_t)(n0 + n) * K + k0 + kk]) : 0.f;
+      if (SWIGLU) w_s[1][kk][n] = live ? to_float(w_e[((size_t)N + n0 + n) * K + k0 + kk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kTileK; ++kk) {
+      const float a0 = a_s[kk][2 * ty], a1 = a_s[kk][2 * ty + 1];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float b = w_s[0][kk][4 * tx + c];
+        acc[0][c] += a0 * b;
+        acc[1][c] += a1 * b;
+        if (SWIGLU) {
+          const float u = w_s[1][kk][4 * tx + c];
+          acc_up[0][c] += a0 * u;
+          acc_up[1][c] += a1 * u;
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int local = 2 * ty + r;
+    if (local >= rows) continue;
+    const int slot = first + local;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int n = n0 + 4 * tx + c;
+      if (n >= N) continue;
+      if (SWIGLU) {
+        out[(size_t)slot * N + n] = from_float<T>(routed_silu(acc[r][c]) * acc_up[r][c]);
+      } else {
+        const float v = scale_out ? acc[r][c] * scale_s[local] : acc[r][c];
+        out32[(size_t)plan.dest[slot] * N + n] = v;
+      }
+    }
+  }
+}
+
+// ---- grouped products on the tensor cores (bfloat16, float32 accumulation) ------------------------------------------
+// The same tiles with 64 rows: a tile of A (gathered rows, scaled and rounded to bfloat16 where the weight is on the
+// input) and a tile of W in shared memory, warp-level matrix products on 16 x 16 x 16 fragments, eight warps as
+// 4 (rows) x 2 (columns) over a 64 x 64 tile (x 2 for gate and up).
+constexpr int kMmaM = 64, kMmaN = 64, kMmaK = 32, kMmaThreads = 256, kMmaPad = 8;
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(kMmaThreads)
+grouped_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const __nv_bfloat16* __restrict__ w,
+                           int* __restrict__ plan_base, int pairs, int experts, __nv_bfloat16* __restrict__ out,
+                           float* __restrict__ out32, int N, int K, int gather, int scale_in, int scale_out) {
+  using namespace nvcuda;
+  const RoutePlan plan = plan_views(plan_base, pairs, experts, kMmaM);
+  const int tile = blockIdx.x;
+  if (tile >= *plan.num_tiles) return;
+  const int expert = plan.tile_expert[tile], first = plan.tile_first[tile], rows = plan.tile_rows[tile];
+  const int n0 = blockIdx.y * kMmaN;
+  __shared__ __align__(32) __nv_bfloat16 a_s[kMmaM][kMmaK + kMmaPad];
+  __shared__ __align__(32) __nv_bfloat16 w_s[SWIGLU ? 2 : 1][kMmaN][kMmaK + kMmaPad];
+  __shared__ __align__(32) float c_s[kMmaThreads / 32][16][16 + 4];
+  __shared__ int src_s[kMmaM];
+  __shared__ float scale_s[kMmaM];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < kMmaM) {
+    const int slot = first + min(tid, rows - 1);
+    src_s[tid] = gather ? plan.source[slot] : slot;
+    scale_s[tid] = plan.scale[slot];
+  }
+  __syncthreads();
+  const int wr = warp >> 1, wc = warp & 1;  // the warp's 16 rows and 32 columns
+  wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[2], acc_up[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) { wmma::fill_fragment(acc[i], 0.f); wmma::fill_fragment(acc_up[i], 0.f); }
+  const size_t w_rows = SWIGLU ? 2 * (size_t)N : (size_t)N;
+  const __nv_bfloat16* w_e = w + (size_t)expert * w_rows * K;
+  for (int k0 = 0; k0 < K; k0 += kMmaK) {
+    // eight elements (16 bytes) a thread: K is a multiple of 8 and rows are 16-byte aligned
+    for (int idx = tid; idx < kMmaM * (kMmaK / 8); idx += kMmaThreads) {
+      const int r = idx / (kMmaK / 8), kk = (idx % (kMmaK / 8)) * 8;
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (r < rows && k0 + kk < K) {
+        raw = *reinterpret_cast<const uint4*>(a + (size_t)src_s[r] * a_stride + k0 + kk);
+        if (scale_in) {
+          float v[8];
+          load8(reinterpret_cast<const __nv_bfloat16*>(&raw), v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] *= scale_s[r];
+          store8(reinterpret_cast<__nv_bfloat16*>(&raw), v);
+        }
+      }
+      *reinterpret_cast<uint4*>(&a_s[r][kk]) = raw;
+    }
+    for (int idx = tid; idx < kMmaN * (kMmaK / 8); idx += kMmaThreads) {
+      const int n = idx / (kMmaK / 8), kk = (idx % (kMmaK / 8)) * 8;
+      const bool live = n0 + n < N && k0 + kk < K;
+      uint4 g = make_uint4(0, 0, 0, 0), u = make_uint4(0, 0, 0, 0);
+      if (live) g = *reinterpret_cast<const uint4*>(w_e + (size_t)(n0 + n) * K + k0 + kk);
+      *reinterpret_cast<uint4*>(&w_s[0][n][kk]) = g;
+      if (SWIGLU) {
+        if (live) u = *reinterpret_cast<const uint4*>(w_e + ((size_t)N + n0 + n) * K + k0 + kk);
+        *reinterpret_cast<uint4*>(&w_s[1][n][kk]) = u;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kMmaK; kk += 16) {
+      wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa;
+      wmma::load_matrix_sync(fa, &a_s[wr * 16][kk], kMmaK + kMmaPad);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> fb;
+        wmma::load_matrix_sync(fb, &w_s[0][wc * 32 + i * 16][kk], kMmaK + kMmaPad);
+        wmma::mma_sync(acc[i], fa, fb, acc[i]);
+        if (SWIGLU) {
+          wmma::load_matrix_sync(fb, &w_s[1][wc * 32 + i * 16][kk], kMmaK + kMmaPad);
+          wmma::mma_sync(acc_up[i], fa, fb, acc_up[i]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (SWIGLU) {
+#pragma unroll
+      for (int e = 0; e < acc[i].num_elements; ++e) acc[i].x[e] = routed_silu(acc[i].x[e]) * acc_up[i].x[e];
+    }
+    wmma::store_matrix_sync(&c_s[warp][0][0], acc[i], 16 + 4, wmma::mem_row_major);
+    __syncwarp();
+    for (int idx = lane; idx < 256; idx += 32) {
+      const int r = idx / 16, c = idx % 16;
+      const int local = wr * 16 + r, n = n0 + wc * 32 + i * 16 + c;
+      if (local < rows && n < N) {
+        const int slot = first + local;
+        const float v = c_s[warp][r][c];
+        if (SWIGLU) out[(size_t)slot * N + n] = __float2bfloat16_rn(v);
+        else out32[(size_t)plan.dest[slot] * N + n] = scale_out ? v * scale_s[local] : v;
+      }
+    }
+    __syncwarp();
+  }
+}
+
+}  // namespace distie
+
+using namespace distie;
+
+// x [tokens, hidden] and router [experts, hidden] of one type; ids, weights [tokens, top].
+extern "C" int distie_route_top(const void* x, int x_stride, const void* router, int tokens, int hidden, int experts,
+                                int top, int* ids, float* weights, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (hidden < 1 || experts < 1 || top < 1 || top > experts || top > kMaxTop || experts > 8192) return DISTIE_ERR_ARG;
+  const size_t shared = (size_t)experts * sizeof(float);
+  if (dtype == DISTIE_BF16)
+    route_top_kernel<<<tokens, kRouteThreads, shared, stream>>>((const __nv_bfloat16*)x, x_stride,
+                                                               (const __nv_bfloat16*)router, hidden, experts, top, ids,
+                                                               weights);
+  else if (dtype == DISTIE_F32)
+    route_top_kernel<<<tokens, kRouteThreads, shared, stream>>>((const float*)x, x_stride, (const float*)router, hidden,
+                                                               experts, top, ids, weights);
+  else
+    return DISTIE_ERR_UNSUPPORTED;
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+// Rows per tile of the grouped products for this type and these sizes (the plan is made for it).
+extern "C" int distie_routed_tile(int dtype, int hidden, int ff) {
+  return (dtype == DISTIE_BF16 && hidden % 8 == 0 && ff % 8 == 0) ? kMmaM : kTileM;
+}
+
+// int32 words of the plan for `pairs` (token, choice) pairs.
+extern "C" long long distie_route_plan_words(int pairs, int experts, int tile) {
+  const long long max_tiles = (pairs + tile - 1) / tile + experts;
+  return 1 + (experts + 1) + 3 * max_tiles + 3LL * pairs;
+}
+
+// x [tokens, hidden]; gate_up [experts, 2 ff, hidden]; down [experts, hidden, ff]; ids, weights [tokens, top];
+// plan: distie_route_plan_words int32; mid [tokens * top, ff] of the type; out [top, tokens, hidden] float32.
+// weight_on_input: the pair's weight multiplies the expert's input, else its output.
+extern "C" int distie_routed_swiglu(const void* x, int x_stride, const int* ids, const float* weights, const void* gate_up,
+                                    const void* down, int* plan, void* mid, float* out, int tokens, int top, int experts,
+                                    int hidden, int ff, int weight_on_input, int dtype, int* error, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (top < 1 || experts < 1 || hidden < 1 || ff < 1 || experts > 4096) return DISTIE_ERR_ARG;
+  if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
+  const int pairs = tokens * top;
+  const int tile = distie_routed_tile(dtype, hidden, ff);
+  const bool mma = tile == kMmaM && x_stride % 8 == 0 &&
+                   (((uintptr_t)x | (uintptr_t)gate_up | (uintptr_t)down | (uintptr_t)mid) & 15) == 0;
+  if (tile == kMmaM && !mma) return DISTIE_ERR_UNSUPPORTED;
+  route_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, weights, tokens, top, experts, tile, plan,
+                                                                           error);
+  DISTIE_LAUNCH_CHECK();
+  const unsigned max_tiles = (unsigned)((pairs + tile - 1) / tile + experts);
+  const int in = weight_on_input ? 1 : 0;
+  if (mma) {
+    const dim3 up_grid(max_tiles, (ff + kMmaN - 1) / kMmaN), down_grid(max_tiles, (hidden + kMmaN - 1) / kMmaN);
+    grouped_product_mma_kernel<true><<<up_grid, kMmaThreads, 0, stream>>>(
+        (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)gate_up, plan, pairs, experts, (__nv_bfloat16*)mid,
+        nullptr, ff, hidden, 1, in, 0);
+    DISTIE_LAUNCH_CHECK();
+    grouped_product_mma_kernel<false><<<down_grid, kMmaThreads, 0, stream>>>(
+        (const __nv_bfloat16*)mid, ff, (const __nv_bfloat16*)down, plan, pairs, experts, nullptr, out, hidden, ff, 0, 0,
+        1 - in);
+    DISTIE_LAUNCH_CHECK();
+    return 0;
+  }
+  const dim3 up_grid(max_tiles, (ff + kTileN - 1) / kTileN), down_grid(max_tiles, (hidden + kTileN - 1) / kTileN);
+  if (dtype == DISTIE_BF16) {
+    grouped_product_kernel<__nv_bfloat16, true><<<up_grid, kGroupedThreads, 0, stream>>>(
+        (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)gate_up, plan, pairs, experts, (__nv_bfloat16*)mid,
+        nullptr, ff, hidden, 1, in, 0);
+    DISTIE_LAUNCH_CHECK();
+    grouped_product_kernel<__nv_bfloat16, false><<<down_grid, kGroupedThreads, 0, stream>>>(
+        (const __nv_bfloat16*)mid, ff, (const __nv_bfloat16*)down, plan, pairs, experts, nullptr, out, hidden, ff, 0, 0,
+        1 - in);
+  } else {
+    grouped_product_kernel<float, true><<<up_grid, kGroupedThreads, 0, stream>>>(
+        (const float*)x, x_stride, (const float*)gate_up, plan, pairs, experts, (float*)mid, nullptr, ff, hidden, 1, in, 0);
+    DISTIE_LAUNCH_CHECK();
+    grouped_product_kernel<float, false><<<down_grid, kGroupedThreads, 0, stream>>>(
+        (const float*)mid, ff, (const float*)down, plan, pairs, experts, nullptr, out, hidden, ff, 0, 0, 1 - in);
+  }
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}

@@ -30,7 +30,7 @@ _SKINNY_ROWS = 64               # weight-streaming products (tcgen05, weights as
 _CLUSTER_SPLITS = 8             # splits of a decode attention that one cluster of CTAs merges itself
 _TENSOR_CORE_ROWS = 128         # from here on the tcgen05 kernel's 128-row tiles are full; in between: the library
 _MAX_TERMS = 24                 # terms of a pending sum that the layer-norm kernel adds up itself
-_RULES = {"delta": 0, "ssd": 1}
+_RULES = {"delta": 0, "ssd": 1, "gated": 2}
 
 _ERROR_TEXT = {
     1: "a token id outside the vocabulary reached the embedding",
@@ -38,6 +38,7 @@ _ERROR_TEXT = {
     3: "a block table does not cover the keys a token attends to",
     4: "a block table does not cover the keys a decoded token attends to",
     6: "a tensor-core product gave up waiting for its own copies or instructions",
+    7: "a router chose an expert that does not exist",
     5: "a block table does not cover the keys a portion of a prompt attends to",
 }
 
@@ -384,16 +385,19 @@ class DeviceKernels(KernelSet):
         self._ran("attention_decode_mma", 1 if splits <= _CLUSTER_SPLITS else 2)
         self._ran("attention_decode_mma_qkv", 0)
 
-    def attention(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale, chunk=None) -> None:
+    def attention(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale, chunk=None,
+                  keep_first=0) -> None:
         window = int(window) if window else 0
         chunk = int(chunk) if chunk else 0
+        keep_first = int(keep_first) if keep_first and window else 0
         value_dim = kv.v.shape[-1]
         same = value_dim == head_dim  # every kernel but the size-agnostic one wants values as large as keys
         n_dec = step.num_decode_tokens if head_dim in _DECODE_HEAD_DIMS and same else 0
         element = qkv.element_size()
         if n_dec > 0:
             splits = self.plan_splits(n_dec, num_heads, num_kv_heads, step.max_kv_len)
-            tensor_cores = self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS
+            # (kept first keys beside a window: the split-KV kernel on the FMA pipe serves them)
+            tensor_cores = self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and not keep_first
             if tensor_cores and splits <= 2 * _CLUSTER_SPLITS:
                 splits = min(splits, _CLUSTER_SPLITS)  # merged inside the kernel, by a cluster of CTAs
             in_kernel_merge = splits == 1 or (tensor_cores and splits <= _CLUSTER_SPLITS)
@@ -406,22 +410,24 @@ class DeviceKernels(KernelSet):
                 scratch.data_ptr() if scratch is not None else None, step.positions.data_ptr(),
                 step.token_seq.data_ptr(), step.seq_seat.data_ptr(), kv.block_table.data_ptr(),
                 kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), n_dec, num_heads, num_kv_heads,
-                head_dim, kv.page_size, kv.num_pages, window, chunk, float(scale), splits,
+                head_dim, kv.page_size, kv.num_pages, window, chunk,
             ]
             if tensor_cores:
                 check(
-                    function("distie_attention_decode_mma")(*head, self.error_flag.data_ptr(), self._stream()),
+                    function("distie_attention_decode_mma")(*head, float(scale), splits, self.error_flag.data_ptr(),
+                                                            self._stream()),
                     "attention_decode_mma",
                 )
             else:
                 check(
-                    function("distie_attention_decode")(*head, self.code, self.error_flag.data_ptr(), self._stream()),
+                    function("distie_attention_decode")(*head, keep_first, float(scale), splits, self.code,
+                                                        self.error_flag.data_ptr(), self._stream()),
                     "attention_decode",
                 )
             self._ran("attention_decode_mma" if tensor_cores else "attention_decode", 1 if in_kernel_merge else 2)
         rest = step.num_tokens - n_dec
         tiled = (rest > 0 and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and step.num_q_tiles
-                 and n_dec == step.num_decode_tokens and same)
+                 and n_dec == step.num_decode_tokens and same and not keep_first)
         if tiled and self._attention_tcgen05(qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, chunk, scale):
             pass
         elif tiled:
@@ -444,7 +450,8 @@ class DeviceKernels(KernelSet):
                     step.positions.data_ptr() + 4 * n_dec, step.token_seq.data_ptr() + 4 * n_dec,
                     step.seq_seat.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[-1],
                     kv.k.data_ptr(), kv.v.data_ptr(), rest, num_heads, num_kv_heads, head_dim, value_dim, kv.page_size,
-                    kv.num_pages, window, chunk, float(scale), self.code, self.error_flag.data_ptr(), self._stream(),
+                    kv.num_pages, window, chunk, keep_first, float(scale), self.code, self.error_flag.data_ptr(),
+                    self._stream(),
                 ),
                 "attention_generic",
             )
@@ -563,11 +570,15 @@ class DeviceKernels(KernelSet):
         return out
 
     def linear_recurrence(self, rule, q, k, v, decay, write, state, step, heads, groups, key_dim, value_dim,
-                          decay_rate=None, decay_bias=None, skip=None):
+                          decay_rate=None, decay_bias=None, skip=None, unit_column=False):
         for name, t in (("q", q), ("k", k), ("v", v)):
             self._rows32(t, f"linear_recurrence {name}")
-        decay_ptr, decay_stride, splits, split_stride = self._sliced(decay, "linear_recurrence decay")
-        write_ptr, write_stride, write_splits, write_split_stride = self._sliced(write, "linear_recurrence write")
+        none = (None, 0, 1, 0)
+        decay_ptr, decay_stride, splits, split_stride = self._sliced(decay, "linear_recurrence decay") if decay is not None else none
+        write_ptr, write_stride, write_splits, write_split_stride = (
+            self._sliced(write, "linear_recurrence write") if write is not None else (None, 0, splits, split_stride))
+        if decay is None:
+            splits, split_stride = write_splits, write_split_stride
         if (splits, split_stride) != (write_splits, write_split_stride):
             raise KernelError("linear_recurrence: decay and write are views of one projection")
         out = torch.empty((step.num_tokens, heads * value_dim), dtype=torch.float32, device=q.device)
@@ -575,28 +586,163 @@ class DeviceKernels(KernelSet):
         check(
             function("distie_linear_recurrence")(
                 _RULES[rule], q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
-                decay_ptr, decay_stride, write_ptr, write_stride, splits, split_stride, decay_rate.data_ptr(),
+                decay_ptr, decay_stride, write_ptr, write_stride, splits, split_stride,
+                decay_rate.data_ptr() if decay_rate is not None else None,
                 decay_bias.data_ptr() if decay_bias is not None else None, skip.data_ptr() if skip is not None else None,
                 state.data_ptr(), out.data_ptr(), out.stride(0), scratch.data_ptr(), self._seq_index(step)[1].data_ptr(),
                 step.seq_seat.data_ptr(), step.num_tokens, step.num_seqs, heads, groups, key_dim, value_dim,
-                self._stream(),
+                int(bool(unit_column)), self._stream(),
             ),
             "linear_recurrence",
         )
         self._ran("linear_recurrence", 2)
         return out
 
-    def gated_rmsnorm(self, x, gate, weight, eps, group, gate_first, out) -> None:
+    def gated_rmsnorm(self, x, gate, weight, eps, group, gate_first, out, activation="silu") -> None:
         self._rows32(x, "gated_rmsnorm x")
         check(
             function("distie_gated_rmsnorm")(
                 x.data_ptr(), x.stride(0), *self._sliced(gate, "gated_rmsnorm gate"), weight.data_ptr(), weight.numel(),
-                out.data_ptr(), out.stride(0), x.shape[0], x.shape[1], group, float(eps), int(bool(gate_first)),
+                out.data_ptr(), out.stride(0), x.shape[0], x.shape[1], group, float(eps),
+                int(bool(gate_first)) | (2 if activation == "sigmoid" else 0),
                 _CODE[out.dtype], self._stream(),
             ),
             "gated_rmsnorm",
         )
         self._ran("gated_rmsnorm")
+
+    # -- norms around a sublayer, keys as values, memories with exponential gates, routed feed-forwards -------------
+    def norm_add_rmsnorm(self, delta, delta_weight, delta_eps, residual, weight, eps, out, rows_index=None) -> None:
+        pairs = [] if delta is None else Terms.of(delta).flat()
+        if len(pairs) > _MAX_TERMS:  # more terms than the kernel takes: the tail is summed here, in float32
+            tail = Terms(pairs[_MAX_TERMS - 1 :]).total()
+            pairs = pairs[: _MAX_TERMS - 1] + [(tail, 1.0)]
+        pairs = [(t if t.is_contiguous() else t.contiguous(), s) for t, s in pairs]
+        pointers = (ctypes.c_void_p * max(1, len(pairs)))(*[t.data_ptr() for t, _ in pairs])
+        scales = (ctypes.c_float * max(1, len(pairs)))(*[s for _, s in pairs])
+        rows = out.shape[0] if out is not None else residual.shape[0]
+        check(
+            function("distie_norm_add_rmsnorm")(
+                pointers, scales, len(pairs), delta_weight.data_ptr() if delta_weight is not None else None,
+                float(delta_eps), residual.data_ptr(), weight.data_ptr() if weight is not None else None, float(eps),
+                out.data_ptr() if out is not None else None, rows_index.data_ptr() if rows_index is not None else None,
+                rows, residual.shape[1], _CODE[out.dtype] if out is not None else self.code, self._stream(),
+            ),
+            "norm_add_rmsnorm",
+        )
+        self._ran("norm_add_rmsnorm")
+
+    def qk_rope_norm_write(self, qk, bias, step, kv, rotary, num_heads, num_kv_heads, head_dim, norm_eps, q_out) -> None:
+        write = kv is not None
+        if write and kv.k.dtype != q_out.dtype:
+            raise KernelError("qk_rope_norm_write: the cache and q are of one type")
+        table = kv.block_table if write else step.seq_seat
+        check(
+            function("distie_qk_rope_norm_write")(
+                *self._sliced(qk, "qk_rope_norm_write"), bias.data_ptr() if bias is not None else None, q_out.data_ptr(),
+                q_out.stride(0), step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
+                table.data_ptr(), table.shape[-1] if write else 1,
+                rotary.inv_freq.data_ptr() if rotary is not None else None,
+                float(rotary.factor) if rotary is not None else 1.0, kv.k.data_ptr() if write else None,
+                kv.v.data_ptr() if write else None, step.num_tokens, num_heads, num_kv_heads, head_dim,
+                rotary.rotary_dim if rotary is not None else 0, int(rotary.interleaved) if rotary is not None else 0,
+                kv.page_size if write else 1, kv.num_pages if write else 1, int(write), int(norm_eps is not None),
+                float(norm_eps or 0.0), _CODE[q_out.dtype], self.error_flag.data_ptr(), self._stream(),
+            ),
+            "qk_rope_norm_write",
+        )
+        self._ran("qk_rope_norm_write")
+
+    def activation(self, x, kind="silu", scale=1.0, scaled_columns=0):
+        if kind not in ("silu", "none"):
+            raise KernelError(f"activation {kind!r}: 'silu' or 'none'")
+        out = torch.empty((x.shape[-2], x.shape[-1]), dtype=torch.float32, device=x.device)
+        check(
+            function("distie_activation")(*self._sliced(x, "activation"), out.data_ptr(), out.shape[0], out.shape[1],
+                                          int(kind == "silu"), float(scale), int(scaled_columns), self._stream()),
+            "activation",
+        )
+        self._ran("activation")
+        return out
+
+    def exp_gate_scan(self, log_in, log_forget, in_bias, forget_bias, cap, state, step):
+        in_ptr, stride, splits, split_stride = self._sliced(log_in, "exp_gate_scan input gate")
+        forget_ptr, forget_stride, forget_splits, forget_split_stride = self._sliced(log_forget, "exp_gate_scan forget gate")
+        if (stride, splits, split_stride) != (forget_stride, forget_splits, forget_split_stride):
+            raise KernelError("exp_gate_scan: the two gates are views of one projection")
+        heads = log_in.shape[-1]
+        gates = torch.empty((3, step.num_tokens, heads), dtype=torch.float32, device=self.device)
+        check(
+            function("distie_exp_gate_scan")(
+                in_ptr, forget_ptr, stride, splits, split_stride, in_bias.data_ptr(), forget_bias.data_ptr(), float(cap),
+                state.data_ptr(), self._seq_index(step)[1].data_ptr(), step.seq_seat.data_ptr(), step.num_seqs, heads,
+                gates[0].data_ptr(), gates[1].data_ptr(), gates[2].data_ptr(), self._stream(),
+            ),
+            "exp_gate_scan",
+        )
+        self._ran("exp_gate_scan")
+        return gates[0], gates[1], gates[2]
+
+    def stabilized_readout(self, read, floor, heads, value_dim):
+        self._rows32(read, "stabilized_readout")
+        if not floor.is_contiguous():
+            raise KernelError("stabilized_readout: a contiguous floor is expected")
+        out = torch.empty((read.shape[0], heads * value_dim), dtype=torch.float32, device=read.device)
+        check(
+            function("distie_stabilized_readout")(read.data_ptr(), read.stride(0), floor.data_ptr(), out.data_ptr(),
+                                                  read.shape[0], heads, value_dim, self._stream()),
+            "stabilized_readout",
+        )
+        self._ran("stabilized_readout")
+        return out
+
+    def route_top(self, x, router, top, scoring="sigmoid"):
+        if scoring != "sigmoid":
+            raise KernelError(f"route_top: scoring {scoring!r} is not built; 'sigmoid' is")
+        library.load_unit("routed")
+        if x.dtype != router.dtype:
+            x = x.to(router.dtype)  # a router kept in 32-bit reads the activations widened
+        if x.stride(1) != 1 or not router.is_contiguous():
+            raise KernelError("route_top: rows with unit column stride are expected")
+        tokens, experts = x.shape[0], router.shape[0]
+        ids = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
+        weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
+        check(
+            function("distie_route_top")(x.data_ptr(), x.stride(0), router.data_ptr(), tokens, x.shape[1], experts, top,
+                                         ids.data_ptr(), weights.data_ptr(), _CODE[x.dtype], self._stream()),
+            "route_top",
+        )
+        self._ran("route_top")
+        return ids, weights
+
+    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input=True):
+        if gate_up.dtype != x.dtype or down.dtype != x.dtype:
+            if gate_up.dtype != down.dtype:
+                raise KernelError("routed_swiglu: the experts' matrices are of one type")
+            x = x.to(gate_up.dtype)
+        if x.stride(1) != 1 or not gate_up.is_contiguous() or not down.is_contiguous():
+            raise KernelError("routed_swiglu: contiguous expert matrices and rows with unit column stride are expected")
+        tokens, top = ids.shape
+        experts, hidden, ff = gate_up.shape[0], x.shape[1], down.shape[2]
+        code = _CODE[x.dtype]
+        if code == 1 and (x.stride(0) % 8 or hidden % 8 or ff % 8):
+            # rows that are no multiples of 16 bytes: the float32 form of the grouped products takes any size
+            x, gate_up, down, code = x.float(), gate_up.float(), down.float(), 0
+        tile = function("distie_routed_tile")(code, hidden, ff)
+        words = function("distie_route_plan_words")(tokens * top, experts, tile)
+        plan = torch.empty(words, dtype=torch.int32, device=x.device)
+        mid = torch.empty((tokens * top, ff), dtype=x.dtype, device=x.device)
+        out = torch.empty((top, tokens, hidden), dtype=torch.float32, device=x.device)
+        check(
+            function("distie_routed_swiglu")(
+                x.data_ptr(), x.stride(0), ids.data_ptr(), weights.data_ptr(), gate_up.data_ptr(), down.data_ptr(),
+                plan.data_ptr(), mid.data_ptr(), out.data_ptr(), tokens, top, experts, hidden, ff, int(bool(scale_input)),
+                code, self.error_flag.data_ptr(), self._stream(),
+            ),
+            "routed_swiglu",
+        )
+        self._ran("routed_swiglu", 3)
+        return out
 
     def sample(self, logits, temperatures, uniforms, out_tokens) -> None:
         check(

@@ -30,8 +30,12 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     ),
     "distie_rope_rows": ("base", [P, P, P, P, I, P, F, I, I, I, I, I, P, P, P, P]),
     "distie_bias_cast": ("base", [P, P, P, L, I, I, P]),
-    "distie_attention_generic": ("base", [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P]),
-    "distie_attention_decode": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P]),
+    "distie_attention_generic": ("base", [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P]),
+    "distie_attention_decode": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, P]),
+    "distie_norm_add_rmsnorm": ("base", [P, P, I, P, F, P, P, F, P, P, I, I, I, P]),
+    "distie_qk_rope_norm_write": (
+        "base", [P, I, I, L, P, P, I, P, P, P, P, I, P, F, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P]
+    ),
     "distie_attention_decode_scratch_floats": ("base", [I, I, I, I]),
     "distie_sample": ("base", [P, L, I, I, P, P, P, P]),
     "distie_attention_prefill": ("bf16", [P, I, P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, P, P]),
@@ -50,15 +54,22 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_seq_index": ("state", [P, I, I, P, P, P]),
     "distie_short_conv": ("state", [P, I, I, L, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),
     "distie_linear_recurrence": (
-        "state", [I, P, I, P, I, P, I, P, I, P, I, I, L, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, P]
+        "state", [I, P, I, P, I, P, I, P, I, P, I, I, L, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, P]
     ),
+    "distie_activation": ("state", [P, I, I, L, P, I, I, I, F, I, P]),
+    "distie_exp_gate_scan": ("state", [P, P, I, I, L, P, P, F, P, P, P, I, I, P, P, P, P]),
+    "distie_stabilized_readout": ("state", [P, I, P, P, I, I, I, P]),
+    "distie_route_top": ("routed", [P, I, P, I, I, I, I, P, P, I, P]),
+    "distie_routed_tile": ("routed", [I, I, I]),
+    "distie_route_plan_words": ("routed", [I, I, I]),
+    "distie_routed_swiglu": ("routed", [P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P]),
     "distie_gated_rmsnorm": ("state", [P, I, P, I, I, L, P, I, P, I, I, I, I, F, I, I, P]),
     "distie_gemm_tcgen05": ("bf16", [P, I, P, P, I, I, I, I, I, I, I, P, P]),
     "distie_gemm_tcgen05_qkv": ("bf16", [P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P]),
     "distie_gemm_tcgen05_skinny_splits": ("bf16", [I, I, I]),
     "distie_gemm_tcgen05_skinny": ("bf16", [P, I, P, P, P, I, I, I, I, I, I, I, P, P]),
 }
-_RESULT = {"distie_attention_decode_scratch_floats": c_longlong}
+_RESULT = {"distie_attention_decode_scratch_floats": c_longlong, "distie_route_plan_words": c_longlong}
 
 _libraries: dict[str, ctypes.CDLL] = {}
 _functions: dict[str, object] = {}
