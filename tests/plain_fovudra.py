@@ -184,3 +184,58 @@ def forward(cfg, w, tokens, dtype=torch.float64, trace=None):
         if trace is not None:
             trace.append(x.clone())
     return zero_centred_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+# -- tensors of a configuration, and random ones ---------------------------------------------------------
+def tensor_shapes(cfg):
+    width, shapes = cfg["width"], {"embed": (cfg["vocab"], cfg["width"]), "embed.norm": (cfg["width"],)}
+    for index, layer in enumerate(cfg["layers"]):
+        p, m = f"l{index}.", layer["mixer"]
+        shapes[p + "norm1"] = shapes[p + "norm1b"] = (width,)
+        q = p + "mix."
+        if layer["type"] == "attention":
+            shapes.update({q + "q": (m["heads"] * m["dim"], width), q + "q.b": (m["heads"] * m["dim"],),
+                           q + "k": (m["kv_heads"] * m["dim"], width), q + "k.b": (m["kv_heads"] * m["dim"],),
+                           q + "o": (width, m["heads"] * m["vdim"])})
+        else:
+            qk, vv = m["heads"] * m["dim"], m["heads"] * m["vdim"]
+            shapes.update({q + "q": (qk, width), q + "k": (qk, width), q + "v": (vv, width), q + "g": (vv, width),
+                           q + "o": (width, vv), q + "norm": (vv,)})
+            if layer["type"] == "mlstm":
+                shapes.update({q + "i": (m["heads"], width), q + "i.b": (m["heads"],), q + "f": (m["heads"], width),
+                               q + "f.b": (m["heads"],)})
+        mlp = layer.get("mlp")
+        if mlp is not None:
+            shapes[p + "norm2"] = shapes[p + "norm2b"] = (width,)
+            q = p + "mlp."
+            shapes[q + "router"] = (mlp["router"]["experts"], width)
+            blocks = [(f"e{e}.", mlp["expert"]["ff"]) for e in range(mlp["router"]["experts"])]
+            if mlp.get("shared") is not None:
+                blocks.append(("shared.", mlp["shared"]["ff"]))
+            for name, ff in blocks:
+                shapes.update({q + name + "gate": (ff, width), q + name + "up": (ff, width), q + name + "down": (width, ff)})
+    shapes["final.norm"] = (width,)
+    shapes["head"] = (cfg["vocab"], width)
+    return shapes
+
+
+def random_weights(cfg, seed, scale=1.0):
+    """Weights rounded to bfloat16 (as checkpoints store them), sized so that activations stay of order one."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(cfg).items():
+        leaf = name.rsplit(".", 1)[-1]
+        if name == "embed":
+            t = torch.randn(shape, generator=g)
+        elif leaf == "router":
+            t = torch.randn(shape, generator=g) * 2.0 / math.sqrt(shape[1])  # scores well apart: no close calls
+        elif len(shape) == 2:
+            t = torch.randn(shape, generator=g) * scale / math.sqrt(shape[1])
+        elif leaf == "b":
+            t = torch.randn(shape, generator=g) * (1.5 if name.endswith(("i.b", "f.b")) else 0.3)
+        elif name.endswith("mix.norm"):
+            t = 1.0 + torch.randn(shape, generator=g) * 0.1
+        else:  # norm scales stored around zero
+            t = torch.randn(shape, generator=g) * 0.1
+        out[name] = t.to(torch.bfloat16).float()
+    return out
