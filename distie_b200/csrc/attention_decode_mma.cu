@@ -103,7 +103,7 @@ attention_decode_mma_kernel(const ProjectionInput proj,
                             const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
                             const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                             int num_heads, int group_size, int head_chunks, int num_kv_heads, int page_size,
-                            int page_shift, int num_pages, int window, int key_chunk, float scale_log2, int cluster_merge,
+                            int page_shift, int num_pages, int window, int key_chunk, int keep_first, float scale_log2, int cluster_merge,
                             int* __restrict__ error) {
   constexpr int CPR = D / 8;                 // 16-byte chunks per row of keys or values
   constexpr int ROW_BYTES = D * 2;
@@ -145,6 +145,7 @@ attention_decode_mma_kernel(const ProjectionInput proj,
   const int split_page = first_page + split * pages_per_split;
   const int lo = max(first, split_page * page_size);
   const int hi = min(pos, (split_page + pages_per_split) * page_size - 1);
+  const int split_lo = lo, split_hi = hi;
   if (FUSED && threadIdx.x < HALF) {  // the angles depend on the position alone, an input of the step
     float sn = 0.f, cs = 1.f;
     if (proj.inv_freq) {
@@ -172,7 +173,7 @@ attention_decode_mma_kernel(const ProjectionInput proj,
   auto page_of = [&](int key) {
     const int column = page_shift >= 0 ? key >> page_shift : key / page_size;
     const int i = column - split_page;
-    if (staged_ready && i < kMmaDecodePages) return sh_pages[i];
+    if (staged_ready && i >= 0 && i < kMmaDecodePages) return sh_pages[i];
     return column < table_width ? table[column] : -1;  // past the end of the table: reported as a missing page
   };
 
@@ -191,14 +192,20 @@ attention_decode_mma_kernel(const ProjectionInput proj,
   }
 
   const int lo16 = lo & ~15;
-  const int groups = hi >= lo ? (hi - lo16) / 16 + 1 : 0;
+  // Groups of 16 keys: those of the split's share of the window first; behind them, in split 0, the groups that
+  // hold the request's first `keep_first` keys when the window has moved past them (keys 0 .. kept - 1).
+  const int kept = split == 0 ? min(keep_first, first) : 0;
+  const int window_groups = hi >= lo ? (hi - lo16) / 16 + 1 : 0;
+  const int groups = window_groups + (kept + 15) / 16;
+  auto group_base = [&](int grp) { return grp < window_groups ? lo16 + grp * 16 : (grp - window_groups) * 16; };
   const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(dyn) + (uint32_t)warp * STAGES * 2 * TILE_BYTES;
   // Issues the copies of one group of 16 keys into a stage of this warp's ring: chunk `id` of the tile
   // (row id / CPR, chunk id % CPR) goes to row * ROW_BYTES + ((chunk ^ (row & 7)) * 16), K and V alike.
   constexpr int RPI = 32 / CPR;  // rows of a tile that one copy instruction of the warp covers
   const int row0 = lane / CPR, ch = lane % CPR;  // this lane's row within those, and its chunk of the row
   auto issue = [&](int grp, int stage) {
-    const int base_key = lo16 + grp * 16;
+    const int base_key = group_base(grp);
+    const int lo = grp < window_groups ? split_lo : 0, hi = grp < window_groups ? split_hi : kept - 1;
     const uint32_t k_dst = my_ring + (uint32_t)stage * 2 * TILE_BYTES, v_dst = k_dst + TILE_BYTES;
     const bool live = grp < groups;
     if (PAGE16) {
@@ -251,7 +258,7 @@ attention_decode_mma_kernel(const ProjectionInput proj,
   int issued = 0;
 #pragma unroll 1
   for (; issued < STAGES - 1; ++issued) {
-    if (lo16 + (warp + issued * kMmaDecodeWarps) * 16 + 15 >= pos) break;
+    if (warp + issued * kMmaDecodeWarps >= window_groups || lo16 + (warp + issued * kMmaDecodeWarps) * 16 + 15 >= pos) break;
     issue(warp + issued * kMmaDecodeWarps, issued);
   }
   grid_dependency_wait();
@@ -344,8 +351,8 @@ attention_decode_mma_kernel(const ProjectionInput proj,
   for (int u = 0; u < kStagedPerThread; ++u) sh_pages[threadIdx.x + u * kMmaDecodeWarps * 32] = staged[u];
   __syncthreads();
   staged_ready = true;
-  const int last_group = groups - 1;
-  const bool owner_warp = owns_new && groups > 0 && warp == last_group % kMmaDecodeWarps;
+  const int last_group = window_groups - 1;
+  const bool owner_warp = owns_new && window_groups > 0 && warp == last_group % kMmaDecodeWarps;
   if (FUSED) {
 #pragma unroll
     for (int nh = 0; nh < NH; ++nh) {
@@ -362,7 +369,8 @@ attention_decode_mma_kernel(const ProjectionInput proj,
   const int lm_mat = lane >> 3, lm_row = lane & 7;
   int stage = 0;
   for (int grp = warp; grp < groups; grp += kMmaDecodeWarps) {
-    const int base_key = lo16 + grp * 16;
+    const int base_key = group_base(grp);
+    const int lo = grp < window_groups ? split_lo : 0, hi = grp < window_groups ? split_hi : kept - 1;
     issue(grp + (STAGES - 1) * kMmaDecodeWarps, (stage + STAGES - 1) % STAGES);  // empty group past the end
     if (STAGES > 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
     else asm volatile("cp.async.wait_group 1;" ::: "memory");
@@ -625,8 +633,10 @@ static int launch_decode_mma(const ProjectionInput* proj, const void* q, int q_r
                              float* scratch, const int* positions, const int* token_seq, const int* seq_seat,
                              const int* block_table, int table_width, const void* k_cache, const void* v_cache,
                              int tokens, int num_heads, int num_kv_heads, int head_dim, int page_size, int num_pages,
-                             int window, int key_chunk, float scale, int num_splits, int* error, cudaStream_t stream) {
+                             int window, int key_chunk, int keep_first, float scale, int num_splits, int* error,
+                             cudaStream_t stream) {
   if (tokens <= 0) return 0;
+  if (keep_first < 0 || (proj && keep_first)) return DISTIE_ERR_ARG;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
       num_splits < 1 || num_splits > 65535 || (num_splits > kMmaDecodeClusterSplits && scratch == nullptr) || (q_row_stride & 7) ||
       (out_row_stride & 3))
@@ -689,7 +699,7 @@ static int launch_decode_mma(const ProjectionInput* proj, const void* q, int q_r
                          shared, stream, projection, (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, \
                          scratch_o, scratch_ml, positions, token_seq, seq_seat, block_table, table_width,          \
                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, num_heads, group, chunks,   \
-                         num_kv_heads, page_size, page_shift, num_pages, window, key_chunk, scale_log2, cluster_merge, error)
+                         num_kv_heads, page_size, page_shift, num_pages, window, key_chunk, keep_first, scale_log2, cluster_merge, error)
 #define DISTIE_MMA_DECODE_BY_STAGES(DV, NV)   \
   if (stages == 2) { DISTIE_MMA_DECODE(DV, 2, NV) } \
   else { DISTIE_MMA_DECODE(DV, 3, NV) }
@@ -722,7 +732,20 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
                                            float scale, int num_splits, int* error, cudaStream_t stream) {
   return launch_decode_mma(nullptr, q, q_row_stride, out, out_row_stride, scratch, positions, token_seq, seq_seat,
                            block_table, table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim,
-                           page_size, num_pages, window, key_chunk, scale, num_splits, error, stream);
+                           page_size, num_pages, window, key_chunk, /*keep_first=*/0, scale, num_splits, error, stream);
+}
+
+// The same with the request's first `keep_first` keys visible beside the window.
+extern "C" int distie_attention_decode_mma_kept(const void* q, int q_row_stride, void* out, int out_row_stride,
+                                                float* scratch, const int* positions, const int* token_seq,
+                                                const int* seq_seat, const int* block_table, int table_width,
+                                                const void* k_cache, const void* v_cache, int tokens, int num_heads,
+                                                int num_kv_heads, int head_dim, int page_size, int num_pages, int window,
+                                                int key_chunk, int keep_first, float scale, int num_splits, int* error,
+                                                cudaStream_t stream) {
+  return launch_decode_mma(nullptr, q, q_row_stride, out, out_row_stride, scratch, positions, token_seq, seq_seat,
+                           block_table, table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim,
+                           page_size, num_pages, window, key_chunk, keep_first, scale, num_splits, error, stream);
 }
 
 // The same for a step of single tokens that starts from the q/k/v projection: `slices` [splits, tokens, row_stride]
@@ -750,5 +773,5 @@ extern "C" int distie_attention_decode_mma_qkv(const float* slices, int splits, 
   proj.write_new = write_new;
   return launch_decode_mma(&proj, nullptr, 8, out, out_row_stride, scratch, positions, token_seq, seq_seat, block_table,
                            table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim, page_size,
-                           num_pages, window, key_chunk, scale, num_splits, error, stream);
+                           num_pages, window, key_chunk, /*keep_first=*/0, scale, num_splits, error, stream);
 }

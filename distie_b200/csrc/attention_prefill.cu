@@ -65,7 +65,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
                          const int* __restrict__ block_table, int table_width,
                          const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                          int group_size, int num_kv_heads, int page_size, int page_shift, int num_pages,
-                         int window, int key_chunk, float scale_log2, int* __restrict__ error) {
+                         int window, int key_chunk, int keep_first, float scale_log2, int* __restrict__ error) {
   constexpr int CHUNKS = D / 8;                       // 16-byte chunks per row
   constexpr int TILE_BYTES = kTileN * D * 2;
   constexpr int ROWS_PER_PASS = kPrefillWarps * 32 / CHUNKS;
@@ -91,7 +91,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
   const int p_last = p0 + rows - 1;
   const int first_key = first_visible_key(p0, window, key_chunk);
   const int kb_start = (first_key / kTileN) * kTileN;
-  const int num_blocks = (p_last - kb_start) / kTileN + 1;
+  // The request's first `keep_first` keys stay visible when the window has moved past them: the blocks that hold
+  // them and lie wholly before the first block of the window come first in the walk.
+  const int kept = min(keep_first, first_key);
+  const int sink_blocks = min((kept + kTileN - 1) / kTileN, kb_start / kTileN);
+  const int num_blocks = sink_blocks + (p_last - kb_start) / kTileN + 1;
+  auto block_key0 = [&](int block) { return block < sink_blocks ? block * kTileN : kb_start + (block - sink_blocks) * kTileN; };
 
   const int my_chunk = threadIdx.x % CHUNKS;
   const int my_row0 = threadIdx.x / CHUNKS;
@@ -106,13 +111,13 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
     }
   };
   auto load_kv = [&](int block, int stage) {
-    const int kb = kb_start + block * kTileN;
+    const int kb = block_key0(block);
 #pragma unroll
     for (int r = my_row0; r < kTileN; r += ROWS_PER_PASS) {
       const int key = kb + r;
       // (keys before every row's window are not looked up: a cache with a window may have given their page
       // back; their rows are filled with zeros and masked)
-      bool ok = key <= p_last && key >= first_key;
+      bool ok = key <= p_last && (key >= first_key || key < kept);
       size_t at = 0;
       if (ok) {
         // page_shift >= 0: the page size is a power of two, so no division per row.
@@ -184,9 +189,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
     // Only blocks that touch the diagonal or the window's edge need the per-element test: a block
     // is wholly visible to this warp when its last key is no later than the warp's first row and
     // its first key is inside the window of the warp's last row.
-    const int kb = kb_start + block * kTileN;
+    const int kb = block_key0(block);
     const int warp_first = p0 + warp * 16, warp_last = warp_first + 15;
-    const bool whole = kb + kTileN - 1 <= warp_first && kb >= first_visible_key(warp_last, window, key_chunk);
+    const bool whole = block >= sink_blocks && kb + kTileN - 1 <= warp_first &&
+                       kb >= first_visible_key(warp_last, window, key_chunk);
     float tile_max[2] = {-INFINITY, -INFINITY};
     if (whole) {
 #pragma unroll
@@ -200,7 +206,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
         for (int r = 0; r < 4; ++r) {
           const int key = kb + i * 8 + 2 * c + (r & 1);
           const int p = pos_row[r >> 1];
-          const bool seen = key <= p && key >= first_visible_key(p, window, key_chunk);
+          const bool seen = key <= p && (key >= first_visible_key(p, window, key_chunk) || key < keep_first);
           s[i][r] = seen ? s[i][r] : -INFINITY;
           tile_max[r >> 1] = fmaxf(tile_max[r >> 1], s[i][r]);
         }
@@ -277,7 +283,8 @@ template <int D>
 int launch_prefill(const void* q, int q_row_stride, void* out, int out_row_stride, const int* q_tiles, int num_tiles,
                    const int* positions, const int* token_seq, const int* seq_seat, const int* block_table,
                    int table_width, const void* k_cache, const void* v_cache, int num_heads, int num_kv_heads,
-                   int page_size, int num_pages, int window, int key_chunk, float scale, int* error, cudaStream_t stream) {
+                   int page_size, int num_pages, int window, int key_chunk, int keep_first, float scale, int* error,
+                   cudaStream_t stream) {
   const int shared = 4 * kTileN * D * 2;
   static bool configured = false;
   if (!configured) {
@@ -293,7 +300,7 @@ int launch_prefill(const void* q, int q_row_stride, void* out, int out_row_strid
   attention_prefill_kernel<D><<<grid, kPrefillWarps * 32, shared, stream>>>(
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, q_tiles, positions, token_seq,
       seq_seat, block_table, table_width, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-      num_heads / num_kv_heads, num_kv_heads, page_size, page_shift, num_pages, window, key_chunk,
+      num_heads / num_kv_heads, num_kv_heads, page_size, page_shift, num_pages, window, key_chunk, keep_first,
       scale * 1.4426950408889634f, error);
   DISTIE_LAUNCH_CHECK();
   return 0;
@@ -310,7 +317,7 @@ extern "C" int distie_attention_prefill(const void* q, int q_row_stride, void* o
                                         const int* q_tiles, int num_tiles, const int* positions,
                                         const int* token_seq, const int* seq_seat, const int* block_table,
                                         int table_width, const void* k_cache, const void* v_cache, int num_heads,
-                                        int num_kv_heads, int head_dim, int page_size, int num_pages, int window, int key_chunk,
+                                        int num_kv_heads, int head_dim, int page_size, int num_pages, int window, int key_chunk, int keep_first,
                                         float scale, int* error, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
@@ -319,7 +326,7 @@ extern "C" int distie_attention_prefill(const void* q, int q_row_stride, void* o
 #define DISTIE_PREFILL(DV)                                                                                        \
   return launch_prefill<DV>(q, q_row_stride, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,       \
                             seq_seat, block_table, table_width, k_cache, v_cache, num_heads, num_kv_heads,        \
-                            page_size, num_pages, window, key_chunk, scale, error, stream)
+                            page_size, num_pages, window, key_chunk, keep_first, scale, error, stream)
   switch (head_dim) {
     case 64: DISTIE_PREFILL(64);
     case 128: DISTIE_PREFILL(128);

@@ -117,7 +117,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  const int* __restrict__ positions, const int* __restrict__ token_seq,
                                  const int* __restrict__ seq_seat, const int* __restrict__ block_table,
                                  int table_width, int group_size, int num_kv_heads, int page_shift, int num_pages,
-                                 int window, int key_chunk, float scale_log2, int* __restrict__ error) {
+                                 int window, int key_chunk, int keep_first, float scale_log2, int* __restrict__ error) {
   extern __shared__ unsigned char raw[];
   auto& sm = *reinterpret_cast<AttnShared<D>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   constexpr int HALVES = D / 64;
@@ -179,22 +179,28 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int last_pos = pos0 + rows - 1;
   const int first_key = first_visible_key(pos0, window, key_chunk);
   const int block_first = first_key / kAttnKeys;
-  const int blocks = last_pos / kAttnKeys - block_first + 1;
+  // With a window that keeps the request's first `keep_first` keys, the blocks that hold those keys and lie wholly
+  // before the window's first block are walked ahead of the window's blocks.
+  const int kept = min(keep_first, first_key);
+  const int sink_blocks = min((kept + kAttnKeys - 1) / kAttnKeys, block_first);
+  const int blocks = sink_blocks + last_pos / kAttnKeys - block_first + 1;
   const int page_size = 1 << page_shift;
   const int* table = block_table + (size_t)seat * table_width;
   const int pages_per_block = kAttnKeys >> page_shift;  // at most 16
-  auto pages_of = [&](int j) {  // pages of block j up to the last one that holds keys the tile needs
-    return min(pages_per_block, ((last_pos - (block_first + j) * kAttnKeys) >> page_shift) + 1);
+  auto block_of = [&](int j) { return j < sink_blocks ? j : block_first + j - sink_blocks; };  // key block of step j
+  auto last_key = [&](int j) { return j < sink_blocks ? kept - 1 : last_pos; };  // last key of it that the tile needs
+  // Page `pg` of block j is fetched when it holds a key some row of the tile sees: one up to the block's last needed
+  // key that lies in the window of the tile's first row or among the kept first keys.  A cache with a window may have
+  // given the other pages back already, so they are neither looked up nor fetched (their rows of the tile are masked
+  // as keys and cleared as values).
+  auto needed = [&](int j, int pg) {
+    const int key0 = block_of(j) * kAttnKeys + (pg << page_shift);
+    return pg < pages_per_block && key0 <= last_key(j) && (key0 + page_size - 1 >= first_key || key0 < kept);
   };
-  // Pages of the first block that lie wholly before the oldest key any row of the tile sees: a cache with a
-  // window may have given them back already, so they are neither looked up nor fetched (their rows of the
-  // tile are masked as keys and cleared as values).
-  const int skipped0 = (first_key - block_first * kAttnKeys) >> page_shift;
-  auto skipped = [&](int j) { return j == 0 ? skipped0 : 0; };
   auto read_table = [&](int j) {  // this lane's page of block j, -1 outside the block's pages
     if (j >= blocks) return -1;
-    const int column = (((block_first + j) * kAttnKeys) >> page_shift) + lane;
-    return (lane >= skipped(j) && lane < pages_of(j) && column < table_width) ? __ldg(table + column) : -1;
+    const int column = ((block_of(j) * kAttnKeys) >> page_shift) + lane;
+    return (needed(j, lane) && column < table_width) ? __ldg(table + column) : -1;
   };
   const bool producer = warp == 0 || warp == kAttnVProducerWarp;
   int page_ahead = producer ? read_table(0) : -1;
@@ -217,16 +223,17 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       const int s = j % stages, use = j / stages;
       const int page = page_ahead;
       page_ahead = read_table(j + 1);
-      const int count = pages_of(j), from = skipped(j);
-      if (__any_sync(0xffffffffu, lane >= from && lane < count && (page < 0 || page >= num_pages))) {
+      const bool mine = needed(j, lane);
+      const int count = __popc(__ballot_sync(0xffffffffu, mine));
+      if (__any_sync(0xffffffffu, mine && (page < 0 || page >= num_pages))) {
         if (lane == 0 && error) atomicExch(error, 5);
         ok = false;
         break;
       }
       if (!__all_sync(0xffffffffu, mbar_wait_unless(&empty[s], (use & 1) ^ 1, failed))) { ok = false; break; }
-      if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)(count - from) * page_size * D * 2);
+      if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)count * page_size * D * 2);
       __syncwarp();
-      if (lane >= from && lane < count) {
+      if (mine) {
         unsigned char* stage = (for_k ? sm.k[s] : sm.v[s]) + lane * page_size * 128;
         const int row = (page * num_kv_heads + kv_head) * page_size;
         for (int h = 0; h < HALVES; ++h) tma_load_2d(stage + h * kAttnHalf, map, &full[s], h * 64, row);
@@ -309,14 +316,14 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     };
     for (int j = 0; j < blocks; ++j) {
       const int s = j & 1, vs = j % kAttnVStages;
-      const int block_key0 = (block_first + j) * kAttnKeys;
+      const int block_key0 = block_of(j) * kAttnKeys;
       const int key0 = block_key0 + g * kAttnGroupKeys;  // first key of this group's part
       const uint32_t s_addr = lane_base + s * kAttnKeys + g * kAttnGroupKeys;
       if (!wait_all(&sm.s_full[s], (j >> 1) & 1)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // No row of the tile needs a mask when every key of the block is old enough and inside every window.
-      const bool unmasked =
-          block_key0 + kAttnKeys - 1 <= pos0 && block_key0 >= first_visible_key(last_pos, window, key_chunk);
+      const bool unmasked = j >= sink_blocks && block_key0 + kAttnKeys - 1 <= pos0 &&
+                            block_key0 >= first_visible_key(last_pos, window, key_chunk);
       uint32_t sv[kAttnGroupKeys];
       tmem_load_64(s_addr, sv);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -324,7 +331,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
         for (int i = 0; i < kAttnGroupKeys; ++i) {
           const int key = key0 + i;
-          if (!(key <= limit && key >= oldest)) sv[i] = 0xff800000u;  // -inf
+          if (!(key <= limit && (key >= oldest || key < keep_first))) sv[i] = 0xff800000u;  // -inf
         }
       }
       // The row's maximum over the group's keys: four running maxima keep the chain of dependent operations short.
@@ -378,13 +385,14 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         l += even + odd;
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      // Rows of V past the last key the tile needs, and rows of pages that were not fetched because they lie
-      // before every row's window: zero, so that P = 0 gives 0.  Each group clears the rows of its own keys.
-      const int first_fetched = block_key0 + (skipped(j) << page_shift);
-      if (block_key0 + kAttnKeys - 1 > last_pos || first_fetched > block_key0) {
+      // Rows of V in pages that were not fetched (past the last key the tile needs, or before every row's window and
+      // not among the kept first keys): zero, so that P = 0 gives 0.  Each group clears the rows of its own keys.
+      bool all_fetched = true;
+      for (int pg = 0; pg < pages_per_block; ++pg) all_fetched = all_fetched && needed(j, pg);
+      if (!all_fetched) {
         if (!wait_all(&sm.v_full[vs], (j / kAttnVStages) & 1)) { ok = false; break; }
         const int row = g * kAttnGroupKeys + (r & (kAttnGroupKeys - 1));
-        if (r < kAttnGroupKeys && (block_key0 + row > last_pos || block_key0 + row < first_fetched)) {
+        if (r < kAttnGroupKeys && !needed(j, row >> page_shift)) {
 #pragma unroll
           for (int h = 0; h < HALVES; ++h) {
             uint4* dst = reinterpret_cast<uint4*>(sm.v[vs] + h * kAttnHalf + row * 128);
@@ -481,7 +489,7 @@ static int launch_attention_tc(const CUtensorMap& map_q, const CUtensorMap& map_
                                const CUtensorMap& map_out, void* out,
                                int out_row_stride, const int* q_tiles, int num_tiles, const int* positions,
                                const int* token_seq, const int* seq_seat, const int* block_table, int table_width,
-                               int num_heads, int num_kv_heads, int page_shift, int num_pages, int window, int key_chunk,
+                               int num_heads, int num_kv_heads, int page_shift, int num_pages, int window, int key_chunk, int keep_first,
                                float scale_log2, int* error, cudaStream_t stream) {
   const size_t shared = sizeof(AttnShared<D>) + 1024;
   static bool configured = false;
@@ -494,7 +502,8 @@ static int launch_attention_tc(const CUtensorMap& map_q, const CUtensorMap& map_
   const cudaError_t err = launch_dependent_family(
       32, attention_prefill_tcgen05_kernel<D>, dim3(num_heads, num_tiles), dim3(kAttnThreads), shared, stream, map_q,
       map_k, map_v, map_out, (__nv_bfloat16*)out, out_row_stride, q_tiles, positions, token_seq, seq_seat, block_table,
-      table_width, num_heads / num_kv_heads, num_kv_heads, page_shift, num_pages, window, key_chunk, scale_log2, error);
+      table_width, num_heads / num_kv_heads, num_kv_heads, page_shift, num_pages, window, key_chunk, keep_first, scale_log2,
+      error);
   return err == cudaSuccess ? 0 : (int)err;
 }
 
@@ -511,11 +520,11 @@ extern "C" int distie_attention_prefill_tcgen05(const void* q, int q_row_stride,
                                                 const int* token_seq, const int* seq_seat, const int* block_table,
                                                 int table_width, const void* k_cache, const void* v_cache, int tokens,
                                                 int num_heads, int num_kv_heads, int head_dim, int page_size,
-                                                int num_pages, int window, int key_chunk, float scale, int* error,
-                                                cudaStream_t stream) {
+                                                int num_pages, int window, int key_chunk, int keep_first, float scale,
+                                                int* error, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (tokens < 1 || num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || table_width < 1 ||
-      num_pages < 1 || num_tiles > 65535)
+      num_pages < 1 || num_tiles > 65535 || keep_first < 0)
     return DISTIE_ERR_ARG;
   if ((head_dim != 64 && head_dim != 128) || page_size < 8 || page_size > 128 || (page_size & (page_size - 1)) ||
       (q_row_stride & 7) || (out_row_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
@@ -535,8 +544,8 @@ extern "C" int distie_attention_prefill_tcgen05(const void* q, int q_row_stride,
   if (head_dim == 64)
     return launch_attention_tc<64>(map_q, map_k, map_v, map_out, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,
                                    seq_seat, block_table, table_width, num_heads, num_kv_heads, page_shift, num_pages,
-                                   window, key_chunk, scale_log2, error, stream);
+                                   window, key_chunk, keep_first, scale_log2, error, stream);
   return launch_attention_tc<128>(map_q, map_k, map_v, map_out, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,
                                   seq_seat, block_table, table_width, num_heads, num_kv_heads, page_shift, num_pages,
-                                  window, key_chunk, scale_log2, error, stream);
+                                  window, key_chunk, keep_first, scale_log2, error, stream);
 }

@@ -396,8 +396,7 @@ class DeviceKernels(KernelSet):
         element = qkv.element_size()
         if n_dec > 0:
             splits = self.plan_splits(n_dec, num_heads, num_kv_heads, step.max_kv_len)
-            # (kept first keys beside a window: the split-KV kernel on the FMA pipe serves them)
-            tensor_cores = self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and not keep_first
+            tensor_cores = self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS
             if tensor_cores and splits <= 2 * _CLUSTER_SPLITS:
                 splits = min(splits, _CLUSTER_SPLITS)  # merged inside the kernel, by a cluster of CTAs
             in_kernel_merge = splits == 1 or (tensor_cores and splits <= _CLUSTER_SPLITS)
@@ -414,8 +413,8 @@ class DeviceKernels(KernelSet):
             ]
             if tensor_cores:
                 check(
-                    function("distie_attention_decode_mma")(*head, float(scale), splits, self.error_flag.data_ptr(),
-                                                            self._stream()),
+                    function("distie_attention_decode_mma_kept")(*head, keep_first, float(scale), splits,
+                                                                 self.error_flag.data_ptr(), self._stream()),
                     "attention_decode_mma",
                 )
             else:
@@ -427,8 +426,9 @@ class DeviceKernels(KernelSet):
             self._ran("attention_decode_mma" if tensor_cores else "attention_decode", 1 if in_kernel_merge else 2)
         rest = step.num_tokens - n_dec
         tiled = (rest > 0 and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and step.num_q_tiles
-                 and n_dec == step.num_decode_tokens and same and not keep_first)
-        if tiled and self._attention_tcgen05(qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, chunk, scale):
+                 and n_dec == step.num_decode_tokens and same)
+        if tiled and self._attention_tcgen05(qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, chunk, scale,
+                                             keep_first):
             pass
         elif tiled:
             check(
@@ -436,7 +436,7 @@ class DeviceKernels(KernelSet):
                     qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), step.q_tiles.data_ptr(),
                     step.num_q_tiles, step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
                     kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), num_heads,
-                    num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, chunk, float(scale),
+                    num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, chunk, keep_first, float(scale),
                     self.error_flag.data_ptr(), self._stream(),
                 ),
                 "attention_prefill",
@@ -457,13 +457,14 @@ class DeviceKernels(KernelSet):
             )
             self._ran("attention_generic")
 
-    def _attention_tcgen05(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, chunk, scale) -> bool:
+    def _attention_tcgen05(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, chunk, scale,
+                           keep_first=0) -> bool:
         """Prompt portions on the tcgen05 kernel; False when it refuses the page size or an alignment."""
         code = function("distie_attention_prefill_tcgen05")(
             qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), step.q_tiles.data_ptr(), step.num_q_tiles,
             step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
             kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), qkv.shape[0],
-            num_heads, num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, chunk, float(scale),
+            num_heads, num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, chunk, keep_first, float(scale),
             self.error_flag.data_ptr(), self._stream(),
         )
         if code == -2:

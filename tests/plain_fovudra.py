@@ -152,9 +152,15 @@ def expert(h, w, p):
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def routed_feed_forward(h, w, p, mlp):
+def routed_feed_forward(h, w, p, mlp, margins=None):
+    """``margins`` (a list) receives, per token, the gap between the logits of the last expert chosen and the first
+    one left out (infinite when every expert is chosen)."""
     experts, top = mlp["router"]["experts"], mlp["router"]["top"]
-    scores = torch.sigmoid(h @ w[p + "router"].T)
+    logits = h @ w[p + "router"].T
+    scores = torch.sigmoid(logits)
+    if margins is not None:
+        ranked = torch.sort(logits, dim=-1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top] if top < experts else torch.full_like(ranked[:, 0], float("inf")))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         chosen = torch.topk(scores[t], top).indices
@@ -169,8 +175,9 @@ def routed_feed_forward(h, w, p, mlp):
 MIXERS = {"attention": attention_mixer, "mlstm": mlstm_mixer, "lightning": lightning_mixer}
 
 
-def forward(cfg, w, tokens, dtype=torch.float64, trace=None):
-    """Logits ``[T, vocab]`` of one sequence; ``trace`` (a list) receives the residual after every layer."""
+def forward(cfg, w, tokens, dtype=torch.float64, trace=None, margins=None):
+    """Logits ``[T, vocab]`` of one sequence; ``trace`` (a list) receives the residual after every layer, ``margins``
+    (a list) every router's margins."""
     w = {name: t.to(dtype) for name, t in w.items() if t.is_floating_point()}
     eps = float(cfg["norm"]["eps"])
     x = zero_centred_norm(w["embed"][torch.as_tensor(tokens, dtype=torch.long)], w["embed.norm"], eps)
@@ -179,7 +186,7 @@ def forward(cfg, w, tokens, dtype=torch.float64, trace=None):
         mixed = MIXERS[layer["type"]](zero_centred_norm(x, w[p + "norm1"], eps), w, p + "mix.", layer["mixer"], eps)
         x = x + zero_centred_norm(mixed, w[p + "norm1b"], eps)
         if layer.get("mlp") is not None:
-            fed = routed_feed_forward(zero_centred_norm(x, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"])
+            fed = routed_feed_forward(zero_centred_norm(x, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"], margins)
             x = x + zero_centred_norm(fed, w[p + "norm2b"], eps)
         if trace is not None:
             trace.append(x.clone())

@@ -138,10 +138,31 @@ def row_errors(have: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
     return diff.pow(2).mean(-1).sqrt() / float(want.double().std())
 
 
-def assert_close(got: dict, expected: dict, tol: float, what: str) -> None:
+CLOSE_CALL = 0.15  # a gap between router logits that 16-bit activations may turn around
+
+
+def close_calls(cfg, weights, requests, kit) -> dict:
+    """Per request, the positions at which some router's choice hangs on less than ``CLOSE_CALL``: the bfloat16
+    engine, whose routers read activations rounded to 16 bits, is not held to the plain choice there (the float32
+    engines are, everywhere)."""
+    if kit.dtype == torch.float32:
+        return {}
+    out = {}
+    for rid, ids in requests.items():
+        margins = []
+        pf.forward(cfg, weights, ids, margins=margins)
+        out[rid] = torch.stack(margins).min(0).values < CLOSE_CALL if margins else torch.zeros(len(ids), dtype=torch.bool)
+    return out
+
+
+def assert_close(got: dict, expected: dict, tol: float, what: str, close: dict | None = None) -> None:
     expected = helpers.expected_for(got, expected)
     for rid, want in expected.items():
         errors = row_errors(got[rid], want)
+        skip = (close or {}).get(rid.split("#")[0])
+        if skip is not None:
+            assert float(skip.double().mean()) < 0.5, f"{what}: request {rid} is mostly close calls"
+            errors = torch.where(skip[: errors.shape[0]], torch.zeros_like(errors), errors)
         at = int(errors.argmax())
         assert float(errors[at]) <= tol, f"{what}: request {rid}, position {at}: {float(errors[at]):.3e} of the logit scale"
 
@@ -555,11 +576,12 @@ def test_one_layer_of_a_kind_prefill_against_single_tokens(kit, kind):
     weights = pf.random_weights(cfg, 40)
     requests = requests_of(cfg, [41, 6], seed=70)
     expected = {rid: plain_logits(cfg, weights, ids) for rid, ids in requests.items()}
+    close = close_calls(cfg, weights, requests, kit)
     for schedule in (helpers.schedule_whole, lambda r: helpers.schedule_tail(r, tail=25)):
         steps = schedule(requests)
         engine = engine_of(cfg, weights, 4, kit, num_blocks=pages_needed(41, 4) + 2, max_seqs=2)
         got = helpers.collect(steps, helpers.run_schedule(TraceSession(engine), steps))
-        assert_close(got, expected, tolerance(kit), kind)
+        assert_close(got, expected, tolerance(kit), kind, close)
 
 
 LENGTHS = {"small": [70, 1, 29, 51], "awkward": [45, 3, 23, 38], "wide": [230, 97, 2, 140], "no_pages": [33, 5, 18]}
@@ -587,13 +609,19 @@ def test_replay_against_plain(kit, name, mode):
     session = TraceSession(engine)
     got = helpers.collect(steps, helpers.run_schedule(session, steps))
     expected = {rid: plain_logits(cfg, weights, ids) for rid, ids in requests.items()}
-    assert_close(got, expected, tolerance(kit), f"{name}/{mode}")
+    assert_close(got, expected, tolerance(kit), f"{name}/{mode}", close_calls(cfg, weights, requests, kit))
     assert engine.cache.free_seats == 3 and all(g.pool.num_free == g.num_pages for g in engine.cache.groups)
     if kit.device.type == "cuda":
         ran = kit.kernel_counts
         assert ran.get("linear_recurrence") and ran.get("norm_add_rmsnorm") and ran.get("routed_swiglu") and ran.get("exp_gate_scan")
         if name != "no_pages":
             assert ran.get("qk_rope_norm_write")
+        if name == "wide" and kit.dtype == torch.bfloat16 and mode != "tail":
+            # head sizes 64 and 128 in bfloat16: prompt portions on the tcgen05 attention, single tokens on the
+            # tensor-core decode attention, kept first keys and all
+            assert ran.get("attention_prefill_tcgen05") and not ran.get("attention_generic"), ran
+            if mode == "mixed":
+                assert ran.get("attention_decode_mma"), ran
 
 
 @pytest.mark.parametrize("name", ["small", "awkward"])
@@ -613,7 +641,7 @@ def test_cuts_at_around_and_across_every_edge(kit, name):
         at += size
     engine, _, _ = engine_for(name, kit, num_blocks=pages_needed(len(ids), page) + 1)
     got = helpers.collect(steps, helpers.run_schedule(TraceSession(engine), steps))
-    assert_close(got, {"a": plain_logits(cfg, weights, ids)}, tolerance(kit), name)
+    assert_close(got, {"a": plain_logits(cfg, weights, ids)}, tolerance(kit), name, close_calls(cfg, weights, {"a": ids}, kit))
 
 
 def test_long_decoding_keeps_the_state(kit):
@@ -636,7 +664,10 @@ def test_long_decoding_keeps_the_state(kit):
     engine, _, _ = engine_for("small", kit, num_blocks=pages_needed(40, page) + 6, max_seqs=2, max_model_len=160)
     got = helpers.collect(steps, helpers.run_schedule(TraceSession(engine), steps))
     want_other = plain_logits(cfg, weights, other)[3::4]
-    assert_close(got, {"long": plain_logits(cfg, weights, long_ids), "o0": want_other, "o1": want_other}, tolerance(kit), "long")
+    close = close_calls(cfg, weights, {"long": long_ids, "o0": other}, kit)
+    if close:
+        close["o0"] = close["o1"] = close["o0"][3::4]
+    assert_close(got, {"long": plain_logits(cfg, weights, long_ids), "o0": want_other, "o1": want_other}, tolerance(kit), "long", close)
     if kit.device.type == "cuda":  # steps of single tokens replayed the captured decode step, state and all
         assert engine.runner.use_graphs and engine.runner.graph_replays >= 100
 
