@@ -32,7 +32,8 @@ tokens, 256 outputs each, 2,048-token step budget, 32 seats) with time to first 
 time per output token, preemptions and the step-time split; ``--dtype fp32`` times the
 true 32-bit engine.  Their caches are sized from free device memory.  ``--compare zelasun`` times the
 Zelasun design beside the Qwen2 decoder at equal width, feed-forward, heads and depth (prefill of 2,048
-tokens, decode steps at ``--batch``; the time of a layer from two depths) and prints a line of its own.
+tokens, decode steps at ``--batch``; the time of a layer from two depths) and prints a line of its own;
+``--compare fovudra`` does the same for the Fovudra design beside Zelasun and Qwen2.
 """
 
 from __future__ import annotations
@@ -237,6 +238,24 @@ def zelasun_config(size: dict, layers: int, chunk: int) -> dict:
             "layers": [pattern[i % 4] for i in range(layers)]}
 
 
+def fovudra_config(size: dict, layers: int, window: int) -> dict:
+    """The Fovudra design at a Qwen2.5 layer's width and heads: heads of 128 in all three mixers, a window of
+    ``window`` keys that keeps the first four, and a routed feed-forward whose active part equals the dense one
+    (16 experts of a quarter of the dense width, three of them per token beside a shared one of the same size)."""
+    heads, kv, quarter = size["heads"], size["kv_heads"], size["ff"] // 4
+    mlp = {"kind": "moe", "router": {"experts": 16, "top": 3}, "expert": {"ff": quarter}, "shared": {"ff": quarter}}
+    attention = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+        "mask": {"size": window, "keep_first": 4},
+        "rot": {"dims": 128, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    lightning = {"type": "lightning", "mlp": mlp, "mixer": {
+        "heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(2 + 6 * h / max(1, heads - 1)) for h in range(heads)]}}
+    mlstm = {"type": "mlstm", "mlp": mlp, "mixer": {"heads": heads, "dim": 128, "vdim": 128, "gate_cap": 15.0}}
+    pattern = [lightning, attention, mlstm, attention]
+    return {"architecture": "Fovudra", "vocab": COMPARE_VOCAB, "width": size["width"], "norm": {"eps": 1e-6},
+            "layers": [pattern[i % 4] for i in range(layers)]}
+
+
 def qwen2_config(size: dict, layers: int) -> dict:
     return {"architectures": ["Qwen2ForCausalLM"], "vocab_size": COMPARE_VOCAB, "hidden_size": size["width"],
             "intermediate_size": size["ff"], "num_hidden_layers": layers, "num_attention_heads": size["heads"],
@@ -245,8 +264,9 @@ def qwen2_config(size: dict, layers: int) -> dict:
 
 
 def compare_designs(args) -> int:
-    """``--compare zelasun``: prefill of 2,048 tokens and decode steps at batch ``--batch`` behind 1,024-token prompts,
-    for the Zelasun design and the Qwen2 decoder at equal width, feed-forward, heads and depth.  Each model is
+    """``--compare zelasun`` (or ``fovudra``): prefill of 2,048 tokens and decode steps at batch ``--batch`` behind
+    1,024-token prompts, for the named design beside the Qwen2 decoder (and, for Fovudra, beside Zelasun, the other
+    design with recurrences) at equal width, feed-forward, heads and depth.  Each model is
     built at two depths (4 and 8 layers) so that the time of a layer is the difference, free of embedding and head.
     One JSON line; not the repository's headline metric."""
     import gc
@@ -260,17 +280,23 @@ def compare_designs(args) -> int:
         names = [args.only_size]
     dtype = "bfloat16" if args.dtype == "bf16" else "float32"
     depths = (4, 8) if args.layers is None else (args.layers,)
-    out = {"compare": "zelasun beside qwen2", "dtype": args.dtype, "batch": args.batch, "prompt_len": PROMPT_LEN,
+    designs = ("zelasun", "qwen2") if args.compare == "zelasun" else ("fovudra", "zelasun", "qwen2")
+    if args.designs:
+        designs = tuple(d for d in designs if d in args.designs.split(","))
+    configs = {"zelasun": lambda size, depth: zelasun_config(size, depth, args.chunk),
+               "fovudra": lambda size, depth: fovudra_config(size, depth, args.chunk),
+               "qwen2": lambda size, depth: qwen2_config(size, depth)}
+    out = {"compare": " beside ".join(designs), "dtype": args.dtype, "batch": args.batch, "prompt_len": PROMPT_LEN,
            "prefill_tokens": PREFILL_TOKENS, "chunk": args.chunk, "sizes": {}}
     pages = 64 * -(-(PROMPT_LEN + args.warmup + args.steps + 2 * 64 + 16) // PAGE) + 2 * (PREFILL_TOKENS // PAGE)
     with ClockSampler() as sampler:
         for name in names:
             size = COMPARE_SIZES[name]
             rows = {}
-            for design in ("zelasun", "qwen2"):
+            for design in designs:
                 point = {}
                 for depth in depths:
-                    raw = zelasun_config(size, depth, args.chunk) if design == "zelasun" else qwen2_config(size, depth)
+                    raw = configs[design](size, depth)
                     engine = build_engine_of(raw, 64, pages, CONTEXT, dtype)
                     burst = DecodeBurst(engine.runner, state_may_repeat=True)
                     entry = {}
@@ -517,9 +543,11 @@ def main() -> int:
     parser.add_argument("--ref-attn", default=None, choices=["auto", "flash", "torch"],
                         help="with --impl reference: its attention backend (default: DISTIE_ATTN, else auto)")
     parser.add_argument("--ref-device", default=None, help=argparse.SUPPRESS)  # "cpu": a dry run of the reference arm
-    parser.add_argument("--compare", default=None, choices=["zelasun"],
+    parser.add_argument("--designs", default=None, help="with --compare: only these of its designs, with commas between them")
+    parser.add_argument("--compare", default=None, choices=["zelasun", "fovudra"],
                         help="time another design beside the Qwen2 decoder at equal layer sizes instead of the default run")
-    parser.add_argument("--chunk", type=int, default=1024, help="with --compare: the chunk of the design's attention")
+    parser.add_argument("--chunk", type=int, default=1024,
+                        help="with --compare: the chunk (Zelasun) or window (Fovudra) of the design's attention")
     parser.add_argument("--only-size", default=None, choices=["1.5b", "7b"], help="with --compare: one of the sizes")
     args = parser.parse_args()
     if args.gpus != 1:

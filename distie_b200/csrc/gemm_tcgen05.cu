@@ -426,6 +426,145 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// The same product over groups of rows that each have a weight matrix of their own (the experts of a routed
+// feed-forward): A holds the rows sorted by group, B the groups' matrices one below the other (`w_rows` rows
+// each), and a list made on the device names the row tiles: (group, first row, rows <= 128) for tile
+// 0 .. *num_m_tiles - 1 (at most `max_m_tiles`).  A tile's box of 128 rows of A may reach into the next group's
+// rows: those rows of the accumulator are not stored.  EPI is GEMM_EPI_SWIGLU (B of a group is [2 inter, K],
+// out[row, inter] bfloat16) or GEMM_EPI_F32 (out[row, N] float32).  Every role skips the tiles past the list's end
+// alike, so the rings stay in step.  Launched the ordinary way: the list comes from the kernel before this one.
+// ---------------------------------------------------------------------------------------------------------------
+struct GroupedTiles {
+  const int* num_m_tiles;
+  const int* group;
+  const int* first;
+  const int* rows;
+  int max_m_tiles;
+  int w_rows;
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(kGemmWideThreads, 1)
+gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                            void* __restrict__ out, int ldo, int N, int K, int inter, int num_tiles,
+                            const GroupedTiles tiles, int* __restrict__ error) {
+  extern __shared__ unsigned char raw[];
+  auto& sm = *reinterpret_cast<GemmShared<BN, STAGES>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t ACC_STRIDE = 256;
+  constexpr uint32_t STAGE_BYTES = (kGemmBM + BN) * kGemmBK * 2;
+  constexpr int PER_TILE = EPI == GEMM_EPI_SWIGLU ? BN / 2 : BN;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k_blocks = (K + kGemmBK - 1) / kGemmBK;
+
+  if (threadIdx.x == 64) {
+    prefetch_tensor_map(&map_a);
+    prefetch_tensor_map(&map_b);
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.accum_full[b], 1);
+      mbar_init(&sm.accum_empty[b], 8);
+    }
+    sm.failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = sm.tmem_base;
+  const int m_tiles = min(*tiles.num_m_tiles, tiles.max_m_tiles);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int mt = tile % tiles.max_m_tiles;
+        if (mt >= m_tiles) continue;
+        const int m0 = tiles.first[mt];
+        const int w0 = tiles.group[mt] * tiles.w_rows + (tile / tiles.max_m_tiles) * PER_TILE;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&sm.empty[s], ((it / STAGES) & 1) ^ 1)) { atomicExch(&sm.failed, 1u); ok = false; break; }
+          mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+          tma_load_2d(sm.b[s], &map_b, &sm.full[s], kb * kGemmBK, w0);
+          if (EPI == GEMM_EPI_SWIGLU)
+            tma_load_2d(sm.b[s] + (BN / 2) * kGemmBK * 2, &map_b, &sm.full[s], kb * kGemmBK, w0 + inter);
+          tma_load_2d(sm.a[s], &map_a, &sm.full[s], kb * kGemmBK, m0);
+        }
+      }
+      if (!ok) {
+        for (uint32_t back = (it > (uint32_t)STAGES ? it - STAGES : 0); back < it; ++back)
+          mbar_wait(&sm.full[back % STAGES], (back / STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BN);
+      uint32_t it = 0, round = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (tile % tiles.max_m_tiles >= m_tiles) continue;
+        const uint32_t buffer = round & 1;
+        if (!mbar_wait(&sm.accum_empty[buffer], ((round >> 1) & 1) ^ 1)) { atomicExch(&sm.failed, 1u); break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem + buffer * ACC_STRIDE;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&sm.full[s], (it / STAGES) & 1)) { atomicExch(&sm.failed, 1u); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t a_desc = smem_desc(sm.a[s]), b_desc = smem_desc(sm.b[s]);
+#pragma unroll
+          for (int k = 0; k < kGemmBK / 16; ++k)
+            umma_bf16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&sm.empty[s]);
+        }
+        umma_commit(&sm.accum_full[buffer]);
+        ++round;
+      }
+    }
+  } else {
+    const int quadrant = warp & 3, part = (warp - 2) >> 2;
+    unsigned char* behind = reinterpret_cast<unsigned char*>(&sm) + ((sizeof(sm) + 15) & ~size_t(15));
+    unsigned char* epilogue_stage = behind + (warp - 2) * kEpilogueStageBytes;
+    uint32_t round = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int mt = tile % tiles.max_m_tiles;
+      if (mt >= m_tiles) continue;
+      const uint32_t buffer = round & 1;
+      const int m0 = tiles.first[mt], rows = tiles.rows[mt];
+      const int n0 = (tile / tiles.max_m_tiles) * PER_TILE;
+      if (!mbar_wait(&sm.accum_full[buffer], (round >> 1) & 1) || sm.failed) { atomicExch(&sm.failed, 1u); break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t lane_base = tmem + buffer * ACC_STRIDE + ((uint32_t)(quadrant * 32) << 16);
+      // (rows of the box past the group's own are not stored: the output ends at row m0 + rows for this tile)
+      store_accumulator<BN, EPI>(lane_base, m0 + quadrant * 32, lane, n0, out, ldo, m0 + rows, N, inter, part, epilogue_stage);
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.accum_empty[buffer]);
+      ++round;
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+  }
+  if (threadIdx.x == 0 && sm.failed && error) atomicExch(error, 6);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 // The same product on pairs of CTAs (clusters of two, tcgen05 with cta_group::2): a pair computes 256 x BN
 // tiles.  Each CTA stages its own 128 rows of A and half of the tile's rows of W, so a stage costs a CTA
 // 16 KB + BN / 2 * 128 bytes instead of 16 KB + BN * 128 for the same number of MMA cycles: the product
@@ -961,6 +1100,58 @@ extern "C" int distie_gemm_tcgen05(const void* x, int ldx, const void* w, void* 
   if (width == 192) { DISTIE_GEMM(192, 5, 4); }
   DISTIE_GEMM(128, 6, 6);
 #undef DISTIE_GEMM
+}
+
+// The grouped product (see gemm_tcgen05_grouped_kernel): a[rows_a, K] sorted by group, w[groups * w_rows, K]; the tile
+// list lives on the device.  epi 2: w_rows = 2 * inter and out[rows_a, inter] bfloat16 = silu(a Wg^T) * (a Wu^T);
+// epi 1: w_rows = N and out[rows_a, N] float32.  K a multiple of 8, rows 16-byte aligned.
+extern "C" int distie_gemm_tcgen05_grouped(const void* a, int lda, int rows_a, const void* w, int groups, int w_rows,
+                                           void* out, int ldo, int N, int K, int epi, const int* num_m_tiles,
+                                           const int* tile_group, const int* tile_first, const int* tile_rows,
+                                           int max_m_tiles, int sm_count, int* error, cudaStream_t stream) {
+  if (rows_a <= 0 || max_m_tiles <= 0) return 0;
+  if (N < 1 || K < 8 || (K & 7) || (lda & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || groups < 1 || w_rows < 1)
+    return DISTIE_ERR_UNSUPPORTED;
+  if ((long long)groups * w_rows > 0x7fffffffLL) return DISTIE_ERR_UNSUPPORTED;
+  if (sm_count < 1) sm_count = 148;
+  CUtensorMap map_a, map_b;
+  int status = make_map(&map_a, a, rows_a, K, lda, kGemmBM);
+  if (status != 0) return status;
+  const GroupedTiles tiles{num_m_tiles, tile_group, tile_first, tile_rows, max_m_tiles, w_rows};
+  if (epi == GEMM_EPI_SWIGLU) {
+    if (w_rows != 2 * N) return DISTIE_ERR_ARG;  // N counts the output columns (inter)
+    if ((status = make_map(&map_b, w, groups * w_rows, K, K, 128)) != 0) return status;
+    const size_t shared = sizeof(GemmShared<256, 4>) + 1024;
+    static bool configured = false;
+    if (!configured) {
+      const cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_grouped_kernel<256, 4, GEMM_EPI_SWIGLU>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+      if (err != cudaSuccess) return (int)err;
+      configured = true;
+    }
+    const int num_tiles = max_m_tiles * ((N + 127) / 128);
+    gemm_tcgen05_grouped_kernel<256, 4, GEMM_EPI_SWIGLU><<<num_tiles < sm_count ? num_tiles : sm_count, kGemmWideThreads,
+                                                           shared, stream>>>(map_a, map_b, out, ldo, 2 * N, K, N, num_tiles,
+                                                                             tiles, error);
+  } else if (epi == GEMM_EPI_F32) {
+    if (w_rows != N) return DISTIE_ERR_ARG;
+    if ((status = make_map(&map_b, w, groups * w_rows, K, K, 128)) != 0) return status;
+    const size_t shared = sizeof(GemmShared<128, 6>) + 1024 + 16 + 8 * kEpilogueStageBytes;
+    static bool configured = false;
+    if (!configured) {
+      const cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_grouped_kernel<128, 6, GEMM_EPI_F32>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+      if (err != cudaSuccess) return (int)err;
+      configured = true;
+    }
+    const int num_tiles = max_m_tiles * ((N + 127) / 128);
+    gemm_tcgen05_grouped_kernel<128, 6, GEMM_EPI_F32><<<num_tiles < sm_count ? num_tiles : sm_count, kGemmWideThreads, shared,
+                                                        stream>>>(map_a, map_b, out, ldo, N, K, 0, num_tiles, tiles, error);
+  } else {
+    return DISTIE_ERR_ARG;
+  }
+  DISTIE_LAUNCH_CHECK();
+  return 0;
 }
 
 // The q/k/v projection of prompt portions with its epilogue fused in: x[M >= 128, K] w[N, K]^T + bias, q and k

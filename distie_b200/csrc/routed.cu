@@ -326,6 +326,30 @@ grouped_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, co
   }
 }
 
+// ---- around the grouped product on the tcgen05 kernel (prompt portions in bfloat16) --------------------------------------
+// gathered[slot, :] = x[source[slot], :] (* scale[slot]): the rows sorted by expert, as the product's A operand.
+template <typename T>
+__global__ void routed_gather_kernel(const T* __restrict__ x, int x_stride, int* __restrict__ plan_base, int pairs,
+                                     int experts, int tile, T* __restrict__ gathered, int hidden, int scale_in) {
+  const RoutePlan plan = plan_views(plan_base, pairs, experts, tile);
+  const int slot = blockIdx.x;
+  const T* src = x + (size_t)plan.source[slot] * x_stride;
+  const float scale = scale_in ? plan.scale[slot] : 1.f;
+  T* dst = gathered + (size_t)slot * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = from_float<T>(to_float(src[c]) * scale);
+}
+
+// out[dest[slot], :] = y[slot, :] (* scale[slot]): the product's rows back in the order [choice, token].
+__global__ void routed_scatter_kernel(const float* __restrict__ y, int* __restrict__ plan_base, int pairs, int experts,
+                                      int tile, float* __restrict__ out, int hidden, int scale_out) {
+  const RoutePlan plan = plan_views(plan_base, pairs, experts, tile);
+  const int slot = blockIdx.x;
+  const float scale = scale_out ? plan.scale[slot] : 1.f;
+  const float* src = y + (size_t)slot * hidden;
+  float* dst = out + (size_t)plan.dest[slot] * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = src[c] * scale;
+}
+
 }  // namespace distie
 
 using namespace distie;
@@ -407,6 +431,40 @@ extern "C" int distie_routed_swiglu(const void* x, int x_stride, const int* ids,
     grouped_product_kernel<float, false><<<down_grid, kGroupedThreads, 0, stream>>>(
         (const float*)mid, ff, (const float*)down, plan, pairs, experts, nullptr, out, hidden, ff, 0, 0, 1 - in);
   }
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+// The plan alone (see route_plan_kernel), for callers that run the grouped products themselves; `tile` rows a tile.
+extern "C" int distie_route_plan(const int* ids, const float* weights, int tokens, int top, int experts, int tile,
+                                 int* plan, int* error, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (top < 1 || experts < 1 || experts > 4096 || tile < 1) return DISTIE_ERR_ARG;
+  route_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, weights, tokens, top, experts, tile, plan,
+                                                                           error);
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int distie_routed_gather(const void* x, int x_stride, int* plan, int pairs, int experts, int tile, void* gathered,
+                                    int hidden, int scale_in, int dtype, cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  if (dtype == DISTIE_BF16)
+    routed_gather_kernel<<<pairs, 256, 0, stream>>>((const __nv_bfloat16*)x, x_stride, plan, pairs, experts, tile,
+                                                   (__nv_bfloat16*)gathered, hidden, scale_in);
+  else if (dtype == DISTIE_F32)
+    routed_gather_kernel<<<pairs, 256, 0, stream>>>((const float*)x, x_stride, plan, pairs, experts, tile, (float*)gathered,
+                                                   hidden, scale_in);
+  else
+    return DISTIE_ERR_UNSUPPORTED;
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int distie_routed_scatter(const float* y, int* plan, int pairs, int experts, int tile, float* out, int hidden,
+                                     int scale_out, cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  routed_scatter_kernel<<<pairs, 256, 0, stream>>>(y, plan, pairs, experts, tile, out, hidden, scale_out);
   DISTIE_LAUNCH_CHECK();
   return 0;
 }

@@ -31,6 +31,7 @@ _CLUSTER_SPLITS = 8             # splits of a decode attention that one cluster 
 _TENSOR_CORE_ROWS = 128         # from here on the tcgen05 kernel's 128-row tiles are full; in between: the library
 _MAX_TERMS = 24                 # terms of a pending sum that the layer-norm kernel adds up itself
 _RULES = {"delta": 0, "ssd": 1, "gated": 2}
+_GROUPED_TENSOR_CORE_PAIRS = 512  # (token, expert) pairs from which the routed products run on the tcgen05 tile kernel
 
 _ERROR_TEXT = {
     1: "a token id outside the vocabulary reached the embedding",
@@ -729,6 +730,8 @@ class DeviceKernels(KernelSet):
         if code == 1 and (x.stride(0) % 8 or hidden % 8 or ff % 8):
             # rows that are no multiples of 16 bytes: the float32 form of the grouped products takes any size
             x, gate_up, down, code = x.float(), gate_up.float(), down.float(), 0
+        if code == 1 and self.dtype == torch.bfloat16 and tokens * top >= _GROUPED_TENSOR_CORE_PAIRS:
+            return self._routed_swiglu_tcgen05(x, ids, weights, gate_up, down, scale_input)
         tile = function("distie_routed_tile")(code, hidden, ff)
         words = function("distie_route_plan_words")(tokens * top, experts, tile)
         plan = torch.empty(words, dtype=torch.int32, device=x.device)
@@ -743,6 +746,38 @@ class DeviceKernels(KernelSet):
             "routed_swiglu",
         )
         self._ran("routed_swiglu", 3)
+        return out
+
+    def _routed_swiglu_tcgen05(self, x, ids, weights, gate_up, down, scale_input):
+        """Prompt portions in bfloat16: the rows sorted by expert (and scaled by their weights) are gathered once, and
+        both products run on the tcgen05 tile kernel over a list of row tiles that stays on the device."""
+        tokens, top = ids.shape
+        experts, hidden, ff = gate_up.shape[0], x.shape[1], down.shape[2]
+        pairs, tile = tokens * top, 128
+        max_tiles = (pairs + tile - 1) // tile + experts
+        words = function("distie_route_plan_words")(pairs, experts, tile)
+        plan = torch.empty(words, dtype=torch.int32, device=x.device)
+        base = plan.data_ptr()
+        tile_expert, tile_first, tile_rows = (base + 4 * (1 + experts + 1 + i * max_tiles) for i in range(3))
+        stream, error = self._stream(), self.error_flag.data_ptr()
+        check(function("distie_route_plan")(ids.data_ptr(), weights.data_ptr(), tokens, top, experts, tile, base, error, stream),
+              "route_plan")
+        gathered = torch.empty((pairs, hidden), dtype=x.dtype, device=x.device)
+        check(function("distie_routed_gather")(x.data_ptr(), x.stride(0), base, pairs, experts, tile, gathered.data_ptr(), hidden,
+                                               int(bool(scale_input)), 1, stream), "routed_gather")
+        mid = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
+        check(function("distie_gemm_tcgen05_grouped")(
+            gathered.data_ptr(), hidden, pairs, gate_up.data_ptr(), experts, 2 * ff, mid.data_ptr(), ff, ff, hidden, 2, base,
+            tile_expert, tile_first, tile_rows, max_tiles, self.sm_count, error, stream), "gemm_tcgen05_grouped")
+        sorted_out = torch.empty((pairs, hidden), dtype=torch.float32, device=x.device)
+        check(function("distie_gemm_tcgen05_grouped")(
+            mid.data_ptr(), ff, pairs, down.data_ptr(), experts, hidden, sorted_out.data_ptr(), hidden, hidden, ff, 1, base,
+            tile_expert, tile_first, tile_rows, max_tiles, self.sm_count, error, stream), "gemm_tcgen05_grouped")
+        out = torch.empty((top, tokens, hidden), dtype=torch.float32, device=x.device)
+        check(function("distie_routed_scatter")(sorted_out.data_ptr(), base, pairs, experts, tile, out.data_ptr(), hidden,
+                                                int(not scale_input), stream), "routed_scatter")
+        self._ran("routed_swiglu", 5)
+        self._ran("gemm_tcgen05_grouped", 0)
         return out
 
     def sample(self, logits, temperatures, uniforms, out_tokens) -> None:

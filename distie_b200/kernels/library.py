@@ -63,6 +63,10 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_route_top": ("routed", [P, I, P, I, I, I, I, P, P, I, P]),
     "distie_routed_tile": ("routed", [I, I, I]),
     "distie_route_plan_words": ("routed", [I, I, I]),
+    "distie_route_plan": ("routed", [P, P, I, I, I, I, P, P, P]),
+    "distie_routed_gather": ("routed", [P, I, P, I, I, I, P, I, I, I, P]),
+    "distie_routed_scatter": ("routed", [P, P, I, I, I, P, I, I, P]),
+    "distie_gemm_tcgen05_grouped": ("bf16", [P, I, I, P, I, I, P, I, I, I, I, P, P, P, P, I, I, P, P]),
     "distie_routed_swiglu": ("routed", [P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P]),
     "distie_gated_rmsnorm": ("state", [P, I, P, I, I, L, P, I, P, I, I, I, I, F, I, I, P]),
     "distie_gemm_tcgen05": ("bf16", [P, I, P, P, I, I, I, I, I, I, I, P, P]),

@@ -30,7 +30,7 @@ def library() -> ctypes.CDLL:
     lib = ctypes.CDLL(build.build_cuda_unit("base"))
     lib.distie_attention_decode_static.argtypes = [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, I, P, P]
     lib.distie_attention_decode_static.restype = I
-    lib.distie_attention_decode.argtypes = [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P]
+    lib.distie_attention_decode.argtypes = [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, P]
     lib.distie_attention_decode.restype = I
     lib.distie_attention_decode_scratch_floats.argtypes = [I, I, I, I]
     lib.distie_attention_decode_scratch_floats.restype = ctypes.c_longlong
@@ -71,8 +71,8 @@ def run(lib, static: bool, q, k, v, table, positions, rows, pages, heads, kv_hea
     else:
         floats = lib.distie_attention_decode_scratch_floats(tokens, heads, head_dim, splits)
         scratch = torch.empty(max(1, floats), dtype=torch.float32, device="cuda")
-        # the allocating entry point also takes a chunk (none here) after the window
-        code = lib.distie_attention_decode(*head, scratch.data_ptr(), *tail[:14], 0, *tail[14:])
+        # the allocating entry point also takes a chunk and a count of kept first keys (none here) after the window
+        code = lib.distie_attention_decode(*head, scratch.data_ptr(), *tail[:14], 0, 0, *tail[14:])
     torch.cuda.synchronize()
     assert int(error.item()) == 0
     return code, out
