@@ -350,6 +350,115 @@ __global__ void routed_scatter_kernel(const float* __restrict__ y, int* __restri
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = src[c] * scale;
 }
 
+// ---- grouped products of steps with few rows per expert: every weight row is streamed once per tile of eight rows -------
+// A tile's rows of A (gathered, scaled) wait in shared memory; a warp takes two weight rows at a time (the gate and the up
+// row of one output column, or two neighbouring columns of the down product), every lane a run of VEC elements of K per
+// round, all loads of a round independent of one another; no barrier inside the walk over K.
+constexpr int kRowsR = 8, kRowsWarps = 8, kRowsPairsPerWarp = 2;
+
+template <typename T, int VEC>
+__device__ __forceinline__ void load_run(const T* p, float (&v)[VEC]) {
+  if constexpr (VEC == 8) load8(p, v);
+  else if constexpr (VEC == 4) { const float4 q = load4(p); v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
+  else v[0] = to_float(p[0]);
+}
+
+template <typename T, bool SWIGLU, int VEC>
+__global__ void __launch_bounds__(kRowsWarps * 32)
+grouped_rows_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ w, int* __restrict__ plan_base, int pairs,
+                    int experts, T* __restrict__ out, float* __restrict__ out32, int N, int K, int gather, int scale_in,
+                    int scale_out) {
+  extern __shared__ __align__(16) unsigned char rows_raw[];
+  T* a_s = reinterpret_cast<T*>(rows_raw);  // [kRowsR][K]
+  __shared__ int src_s[kRowsR];
+  __shared__ float scale_s[kRowsR];
+  const RoutePlan plan = plan_views(plan_base, pairs, experts, kRowsR);
+  const int tile = blockIdx.x;
+  if (tile >= *plan.num_tiles) return;
+  const int expert = plan.tile_expert[tile], first = plan.tile_first[tile], rows = plan.tile_rows[tile];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < kRowsR) {
+    const int slot = first + min(tid, rows - 1);
+    src_s[tid] = gather ? plan.source[slot] : slot;
+    scale_s[tid] = plan.scale[slot];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rows * K; idx += kRowsWarps * 32) {
+    const int r = idx / K, k = idx - r * K;
+    float v = to_float(a[(size_t)src_s[r] * a_stride + k]);
+    if (scale_in) v *= scale_s[r];
+    a_s[(size_t)r * K + k] = from_float<T>(v);  // the expert reads weight * x in the engine's type
+  }
+  __syncthreads();
+  const size_t w_rows = SWIGLU ? 2 * (size_t)N : (size_t)N;
+  const T* w_e = w + (size_t)expert * w_rows * K;
+  constexpr int COLS = SWIGLU ? 1 : 2;  // output columns a warp finishes per round
+  const int col0 = (blockIdx.y * kRowsWarps * kRowsPairsPerWarp + warp * kRowsPairsPerWarp) * COLS;
+#pragma unroll 1
+  for (int round = 0; round < kRowsPairsPerWarp; ++round) {
+    const int n = col0 + round * COLS;
+    if (n >= N) break;
+    const bool second = SWIGLU || n + 1 < N;
+    const T* w0 = w_e + (size_t)n * K;
+    const T* w1 = w_e + (SWIGLU ? (size_t)N + n : (second ? (size_t)n + 1 : (size_t)n)) * K;
+    float acc0[kRowsR], acc1[kRowsR];
+#pragma unroll
+    for (int r = 0; r < kRowsR; ++r) acc0[r] = acc1[r] = 0.f;
+    for (int k = lane * VEC; k < K; k += 32 * VEC) {
+      float x0[VEC], x1[VEC];
+      load_run<T, VEC>(w0 + k, x0);
+      load_run<T, VEC>(w1 + k, x1);
+#pragma unroll
+      for (int r = 0; r < kRowsR; ++r) {
+        if (r < rows) {
+          float av[VEC];
+          load_run<T, VEC>(a_s + (size_t)r * K + k, av);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) { acc0[r] += av[i] * x0[i]; acc1[r] += av[i] * x1[i]; }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kRowsR; ++r) {
+      if (r < rows) { acc0[r] = warp_sum(acc0[r]); acc1[r] = warp_sum(acc1[r]); }
+    }
+    if (lane < rows) {
+      float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+      for (int r = 0; r < kRowsR; ++r)
+        if (r == lane) { v0 = acc0[r]; v1 = acc1[r]; }
+      const int slot = first + lane;
+      if (SWIGLU) {
+        out[(size_t)slot * N + n] = from_float<T>(routed_silu(v0) * v1);
+      } else {
+        const float s = scale_out ? scale_s[lane] : 1.f;
+        float* dst = out32 + (size_t)plan.dest[slot] * N + n;
+        dst[0] = v0 * s;
+        if (second) dst[1] = v1 * s;
+      }
+    }
+  }
+}
+
+template <typename T, bool SWIGLU>
+static int launch_grouped_rows(const T* a, int a_stride, const T* w, int* plan, int pairs, int experts, T* out, float* out32,
+                               int N, int K, int gather, int scale_in, int scale_out, unsigned max_tiles, cudaStream_t stream) {
+  constexpr int WIDE = sizeof(T) == 2 ? 8 : 4;
+  const bool vec = K % WIDE == 0 && a_stride % WIDE == 0 && (((uintptr_t)a | (uintptr_t)w) & 15) == 0;
+  const size_t shared = (size_t)kRowsR * K * sizeof(T);
+  const int per_block = kRowsWarps * kRowsPairsPerWarp * (SWIGLU ? 1 : 2);
+  const dim3 grid(max_tiles, (N + per_block - 1) / per_block);
+  auto run = [&](auto kernel) {
+    if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    kernel<<<grid, kRowsWarps * 32, shared, stream>>>(a, a_stride, w, plan, pairs, experts, out, out32, N, K, gather, scale_in,
+                                                     scale_out);
+  };
+  if (vec) run(grouped_rows_kernel<T, SWIGLU, WIDE>);
+  else run(grouped_rows_kernel<T, SWIGLU, 1>);
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
 }  // namespace distie
 
 using namespace distie;
@@ -373,8 +482,11 @@ extern "C" int distie_route_top(const void* x, int x_stride, const void* router,
   return 0;
 }
 
-// Rows per tile of the grouped products for this type and these sizes (the plan is made for it).
-extern "C" int distie_routed_tile(int dtype, int hidden, int ff) {
+// Rows per tile of the grouped products for this type and these sizes (the plan is made for it): few rows per
+// expert stream the weights past tiles of eight rows; more go to tiles of 64 (tensor cores) or 32 (FMA pipe).
+extern "C" int distie_routed_tile(int dtype, int hidden, int ff, int pairs, int experts) {
+  const int widest = hidden > ff ? hidden : ff;
+  if (pairs <= 16 * experts && (size_t)kRowsR * widest * (dtype == DISTIE_BF16 ? 2 : 4) <= 160 * 1024) return kRowsR;
   return (dtype == DISTIE_BF16 && hidden % 8 == 0 && ff % 8 == 0) ? kMmaM : kTileM;
 }
 
@@ -394,7 +506,7 @@ extern "C" int distie_routed_swiglu(const void* x, int x_stride, const int* ids,
   if (top < 1 || experts < 1 || hidden < 1 || ff < 1 || experts > 4096) return DISTIE_ERR_ARG;
   if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
   const int pairs = tokens * top;
-  const int tile = distie_routed_tile(dtype, hidden, ff);
+  const int tile = distie_routed_tile(dtype, hidden, ff, pairs, experts);
   const bool mma = tile == kMmaM && x_stride % 8 == 0 &&
                    (((uintptr_t)x | (uintptr_t)gate_up | (uintptr_t)down | (uintptr_t)mid) & 15) == 0;
   if (tile == kMmaM && !mma) return DISTIE_ERR_UNSUPPORTED;
@@ -403,6 +515,22 @@ extern "C" int distie_routed_swiglu(const void* x, int x_stride, const int* ids,
   DISTIE_LAUNCH_CHECK();
   const unsigned max_tiles = (unsigned)((pairs + tile - 1) / tile + experts);
   const int in = weight_on_input ? 1 : 0;
+  if (tile == kRowsR) {
+    int status;
+    if (dtype == DISTIE_BF16) {
+      status = launch_grouped_rows<__nv_bfloat16, true>((const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)gate_up, plan,
+                                                        pairs, experts, (__nv_bfloat16*)mid, nullptr, ff, hidden, 1, in, 0,
+                                                        max_tiles, stream);
+      if (status != 0) return status;
+      return launch_grouped_rows<__nv_bfloat16, false>((const __nv_bfloat16*)mid, ff, (const __nv_bfloat16*)down, plan, pairs,
+                                                       experts, nullptr, out, hidden, ff, 0, 0, 1 - in, max_tiles, stream);
+    }
+    status = launch_grouped_rows<float, true>((const float*)x, x_stride, (const float*)gate_up, plan, pairs, experts,
+                                              (float*)mid, nullptr, ff, hidden, 1, in, 0, max_tiles, stream);
+    if (status != 0) return status;
+    return launch_grouped_rows<float, false>((const float*)mid, ff, (const float*)down, plan, pairs, experts, nullptr, out,
+                                             hidden, ff, 0, 0, 1 - in, max_tiles, stream);
+  }
   if (mma) {
     const dim3 up_grid(max_tiles, (ff + kMmaN - 1) / kMmaN), down_grid(max_tiles, (hidden + kMmaN - 1) / kMmaN);
     grouped_product_mma_kernel<true><<<up_grid, kMmaThreads, 0, stream>>>(

@@ -732,7 +732,7 @@ class DeviceKernels(KernelSet):
             x, gate_up, down, code = x.float(), gate_up.float(), down.float(), 0
         if code == 1 and self.dtype == torch.bfloat16 and tokens * top >= _GROUPED_TENSOR_CORE_PAIRS:
             return self._routed_swiglu_tcgen05(x, ids, weights, gate_up, down, scale_input)
-        tile = function("distie_routed_tile")(code, hidden, ff)
+        tile = function("distie_routed_tile")(code, hidden, ff, tokens * top, experts)
         words = function("distie_route_plan_words")(tokens * top, experts, tile)
         plan = torch.empty(words, dtype=torch.int32, device=x.device)
         mid = torch.empty((tokens * top, ff), dtype=x.dtype, device=x.device)

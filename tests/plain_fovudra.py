@@ -235,7 +235,7 @@ def random_weights(cfg, seed, scale=1.0):
         if name == "embed":
             t = torch.randn(shape, generator=g)
         elif leaf == "router":
-            t = torch.randn(shape, generator=g) * 2.0 / math.sqrt(shape[1])  # scores well apart: no close calls
+            t = torch.randn(shape, generator=g) * 6.0 / math.sqrt(shape[1])  # scores well apart: few close calls
         elif len(shape) == 2:
             t = torch.randn(shape, generator=g) * scale / math.sqrt(shape[1])
         elif leaf == "b":
