@@ -15,6 +15,31 @@ import math
 import torch
 
 
+STORED = None  # a torch dtype: what an engine of that type hands from one product to the next is rounded to it
+
+
+def stored(x):
+    """``x`` as a 16-bit engine stores it between two products (norm outputs, q, k and v, gated read-outs, what an
+    expert reads and what it hands to its down projection); unchanged unless :func:`stored_as` is active."""
+    return x if STORED is None else x.to(STORED).to(x.dtype)
+
+
+class stored_as:
+    """``with stored_as(torch.bfloat16): forward(...)``: the plain implementation with the roundings of a 16-bit engine
+    (everything else stays in the precision of the call): what such an engine may lose, and nothing more."""
+
+    def __init__(self, dtype):
+        self.dtype = dtype
+
+    def __enter__(self):
+        global STORED
+        self.before, STORED = STORED, self.dtype
+
+    def __exit__(self, *exc):
+        global STORED
+        STORED = self.before
+
+
 def silu(z):
     return z * torch.sigmoid(z)
 
@@ -26,6 +51,11 @@ def rms_unit(x, eps):
 def zero_centred_norm(x, weight, eps):
     """RMS norm whose weight is stored around zero."""
     return rms_unit(x, eps) * (1.0 + weight)
+
+
+def normed_input(x, weight, eps):
+    """What a sublayer reads: the norm of the residual, as the engine stores it."""
+    return stored(zero_centred_norm(x, weight, eps))
 
 
 # -- rotary positions with scaled frequencies ------------------------------------------------------
@@ -86,14 +116,14 @@ def attention_mixer(h, w, p, m, eps):
         raise ValueError("the values are the keys: vdim equals dim")
     q = (h @ w[p + "q"].T + w[p + "q.b"]).reshape(tokens, heads, dim)
     k = (h @ w[p + "k"].T + w[p + "k.b"]).reshape(tokens, kv_heads, dim)
-    v = k.clone()
+    v = stored(k)
     rot = m["rot"]
     freqs = rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling"), h.dtype)
     positions = torch.arange(tokens)
-    q = rms_unit(rotate_half(q, positions, freqs, rot["dims"]), eps)
-    k = rms_unit(rotate_half(k, positions, freqs, rot["dims"]), eps)
+    q = stored(rms_unit(rotate_half(q, positions, freqs, rot["dims"]), eps))
+    k = stored(rms_unit(rotate_half(k, positions, freqs, rot["dims"]), eps))
     o = windowed_softmax(q, k, v, m["scale"], m["mask"]["size"], m["mask"]["keep_first"])
-    return o.reshape(tokens, heads * dim) @ w[p + "o"].T
+    return stored(o.reshape(tokens, heads * dim)) @ w[p + "o"].T
 
 
 # -- matrix memory with exponential gates --------------------------------------------------------------
@@ -125,7 +155,7 @@ def mlstm_mixer(h, w, p, m, eps):
             out[t, head] = (S.T @ q[t, head]) / (floor + 1e-6)
     out = rms_unit(out, eps).reshape(tokens, heads * vdim) * w[p + "norm"]
     out = out * torch.sigmoid(h @ w[p + "g"].T)
-    return out @ w[p + "o"].T
+    return stored(out) @ w[p + "o"].T
 
 
 # -- linear attention with a fixed decay per head -------------------------------------------------------
@@ -144,12 +174,13 @@ def lightning_mixer(h, w, p, m, eps):
             out[t, head] = S.T @ q[t, head]
     out = rms_unit(out.reshape(tokens, heads * vdim), eps) * w[p + "norm"]
     out = out * torch.sigmoid(h @ w[p + "g"].T)
-    return out @ w[p + "o"].T
+    return stored(out) @ w[p + "o"].T
 
 
 # -- routed feed-forward ---------------------------------------------------------------------------------
 def expert(h, w, p):
-    return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
+    h = stored(h)
+    return stored(silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
 def routed_feed_forward(h, w, p, mlp, margins=None):
@@ -183,14 +214,14 @@ def forward(cfg, w, tokens, dtype=torch.float64, trace=None, margins=None):
     x = zero_centred_norm(w["embed"][torch.as_tensor(tokens, dtype=torch.long)], w["embed.norm"], eps)
     for index, layer in enumerate(cfg["layers"]):
         p = f"l{index}."
-        mixed = MIXERS[layer["type"]](zero_centred_norm(x, w[p + "norm1"], eps), w, p + "mix.", layer["mixer"], eps)
+        mixed = MIXERS[layer["type"]](normed_input(x, w[p + "norm1"], eps), w, p + "mix.", layer["mixer"], eps)
         x = x + zero_centred_norm(mixed, w[p + "norm1b"], eps)
         if layer.get("mlp") is not None:
-            fed = routed_feed_forward(zero_centred_norm(x, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"], margins)
+            fed = routed_feed_forward(normed_input(x, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"], margins)
             x = x + zero_centred_norm(fed, w[p + "norm2b"], eps)
         if trace is not None:
             trace.append(x.clone())
-    return zero_centred_norm(x, w["final.norm"], eps) @ w["head"].T
+    return normed_input(x, w["final.norm"], eps) @ w["head"].T
 
 
 # -- tensors of a configuration, and random ones ---------------------------------------------------------
