@@ -1135,17 +1135,17 @@ extern "C" int distie_gemm_tcgen05_grouped(const void* a, int lda, int rows_a, c
                                                                              tiles, error);
   } else if (epi == GEMM_EPI_F32) {
     if (w_rows != N) return DISTIE_ERR_ARG;
-    if ((status = make_map(&map_b, w, groups * w_rows, K, K, 128)) != 0) return status;
-    const size_t shared = sizeof(GemmShared<128, 6>) + 1024 + 16 + 8 * kEpilogueStageBytes;
+    if ((status = make_map(&map_b, w, groups * w_rows, K, K, 256)) != 0) return status;
+    const size_t shared = sizeof(GemmShared<256, 4>) + 1024 + 16 + 8 * kEpilogueStageBytes;
     static bool configured = false;
     if (!configured) {
-      const cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_grouped_kernel<128, 6, GEMM_EPI_F32>,
+      const cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_grouped_kernel<256, 4, GEMM_EPI_F32>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
       if (err != cudaSuccess) return (int)err;
       configured = true;
     }
-    const int num_tiles = max_m_tiles * ((N + 127) / 128);
-    gemm_tcgen05_grouped_kernel<128, 6, GEMM_EPI_F32><<<num_tiles < sm_count ? num_tiles : sm_count, kGemmWideThreads, shared,
+    const int num_tiles = max_m_tiles * ((N + 255) / 256);
+    gemm_tcgen05_grouped_kernel<256, 4, GEMM_EPI_F32><<<num_tiles < sm_count ? num_tiles : sm_count, kGemmWideThreads, shared,
                                                         stream>>>(map_a, map_b, out, ldo, N, K, 0, num_tiles, tiles, error);
   } else {
     return DISTIE_ERR_ARG;

@@ -61,6 +61,65 @@ norm_add_rmsnorm_kernel(ResidualTerms terms, const float* __restrict__ delta_wei
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) out_row[c] = from_float<T>(row_s[c] * unit * weight[c]);
 }
 
+// The same with four columns a thread and the row in registers: hidden a multiple of 4 and at most
+// 4 * PIECES * blockDim.x, every pointer 16-byte aligned.  All loads of a row's terms are in flight together.
+template <typename T, int PIECES>
+__global__ void __launch_bounds__(512)
+norm_add_rmsnorm_vec_kernel(ResidualTerms terms, const float* __restrict__ delta_weight, float delta_eps,
+                            float* __restrict__ residual, const float* __restrict__ weight, float eps,
+                            T* __restrict__ out, const int* __restrict__ rows_index, int hidden) {
+  __shared__ float scratch[32];
+  const int i = blockIdx.x;
+  const size_t row = rows_index ? (size_t)rows_index[i] : (size_t)i;
+  float* res = residual + row * hidden;
+  float4 r[PIECES], d[PIECES];
+  float ss = 0.f;
+#pragma unroll
+  for (int p = 0; p < PIECES; ++p) {
+    const int c = (p * blockDim.x + threadIdx.x) * 4;
+    d[p] = make_float4(0.f, 0.f, 0.f, 0.f);
+    r[p] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < hidden) {
+      r[p] = *reinterpret_cast<const float4*>(res + c);
+      for (int j = 0; j < terms.count; ++j) {
+        const float4 v = *reinterpret_cast<const float4*>(terms.ptr[j] + row * hidden + c);
+        const float s = terms.scale[j];
+        d[p].x += s * v.x; d[p].y += s * v.y; d[p].z += s * v.z; d[p].w += s * v.w;
+      }
+      ss += (d[p].x * d[p].x + d[p].y * d[p].y) + (d[p].z * d[p].z + d[p].w * d[p].w);
+    }
+  }
+  if (terms.count > 0) {
+    float factor = 1.f;
+    if (delta_weight) factor = rsqrtf(block_sum(ss, scratch) / (float)hidden + delta_eps);
+#pragma unroll
+    for (int p = 0; p < PIECES; ++p) {
+      const int c = (p * blockDim.x + threadIdx.x) * 4;
+      if (c < hidden) {
+        float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (delta_weight) w = *reinterpret_cast<const float4*>(delta_weight + c);
+        r[p].x += d[p].x * factor * w.x; r[p].y += d[p].y * factor * w.y;
+        r[p].z += d[p].z * factor * w.z; r[p].w += d[p].w * factor * w.w;
+        if (!rows_index) *reinterpret_cast<float4*>(res + c) = r[p];
+      }
+    }
+  }
+  if (!out) return;
+  ss = 0.f;
+#pragma unroll
+  for (int p = 0; p < PIECES; ++p) ss += (r[p].x * r[p].x + r[p].y * r[p].y) + (r[p].z * r[p].z + r[p].w * r[p].w);
+  const float unit = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+  T* out_row = out + (size_t)i * hidden;
+#pragma unroll
+  for (int p = 0; p < PIECES; ++p) {
+    const int c = (p * blockDim.x + threadIdx.x) * 4;
+    if (c < hidden) {
+      const float4 w = *reinterpret_cast<const float4*>(weight + c);
+      store4(out_row + c, make_float4(r[p].x * unit * w.x, r[p].y * unit * w.y, r[p].z * unit * w.z, r[p].w * unit * w.w));
+    }
+  }
+}
+
 struct SlicedRows {
   const float* p;
   int stride;
@@ -147,6 +206,27 @@ extern "C" int distie_norm_add_rmsnorm(const float* const* term_ptrs, const floa
   ResidualTerms terms;
   terms.count = num_terms;
   for (int j = 0; j < num_terms; ++j) { terms.ptr[j] = term_ptrs[j]; terms.scale[j] = term_scales[j]; }
+  uintptr_t low_bits = (uintptr_t)residual | (uintptr_t)weight | (uintptr_t)delta_weight | (uintptr_t)out;
+  for (int j = 0; j < num_terms; ++j) low_bits |= (uintptr_t)term_ptrs[j];
+  if (hidden % 4 == 0 && hidden <= 4 * 4 * 512 && (low_bits & 15) == 0 && (dtype == DISTIE_BF16 || dtype == DISTIE_F32)) {
+    const int quads = hidden / 4;
+    int vec_threads = 32;
+    while (vec_threads < 512 && vec_threads < quads) vec_threads *= 2;
+    const int pieces = (quads + vec_threads - 1) / vec_threads;
+#define DISTIE_NORM_VEC(T, PIECESV)                                                                                       \
+  norm_add_rmsnorm_vec_kernel<T, PIECESV><<<rows, vec_threads, 0, stream>>>(terms, delta_weight, delta_eps, residual, weight, \
+                                                                            eps, (T*)out, rows_index, hidden)
+    if (dtype == DISTIE_BF16) {
+      if (pieces == 1) DISTIE_NORM_VEC(__nv_bfloat16, 1); else if (pieces == 2) DISTIE_NORM_VEC(__nv_bfloat16, 2);
+      else DISTIE_NORM_VEC(__nv_bfloat16, 4);
+    } else {
+      if (pieces == 1) DISTIE_NORM_VEC(float, 1); else if (pieces == 2) DISTIE_NORM_VEC(float, 2);
+      else DISTIE_NORM_VEC(float, 4);
+    }
+#undef DISTIE_NORM_VEC
+    DISTIE_LAUNCH_CHECK();
+    return 0;
+  }
   const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
   const size_t shared = (size_t)hidden * sizeof(float);
   if (shared > 200 * 1024) return DISTIE_ERR_UNSUPPORTED;

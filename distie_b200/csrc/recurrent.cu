@@ -754,46 +754,59 @@ __global__ void activation_kernel(Sliced x, float* __restrict__ out, int tokens,
 // Exponential gates under a running maximum, one block per request of the step:
 //   i = cap tanh((x_i + b_i) / cap);  f = logsigmoid(cap tanh((x_f + b_f) / cap));  m_t = max(f_t + m_(t-1), i_t)
 //   keep = exp(f + m_(t-1) - m_t);  take = exp(i - m_t);  floor = exp(-m_t);  m lives in state[seat, head].
-// Three passes: the gates of all tokens side by side, the maximum token by token (a thread per head: two additions
-// and a maximum per token on the chain), the exponentials side by side again.
+// The request's tokens go through shared memory in tiles: the gates of a tile side by side, then the maximum token
+// by token (a thread per head: an addition and a maximum per token on the chain, its operands already on the chip),
+// then the exponentials side by side and out.  The walk is the plain sequence of operations whatever the tile or the
+// cutting of the prompt, so its results depend on neither.
+// gates_s: 3 * tile_tokens * heads floats of dynamic shared memory.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 exp_gate_scan_kernel(Sliced log_in, Sliced log_forget, const float* __restrict__ in_bias,
                      const float* __restrict__ forget_bias, float cap, float* __restrict__ state,
-                     const int* __restrict__ seq_bounds, const int* __restrict__ seq_seat, int heads,
+                     const int* __restrict__ seq_bounds, const int* __restrict__ seq_seat, int heads, int tile_tokens,
                      float* __restrict__ keep, float* __restrict__ take, float* __restrict__ floor_out) {
+  extern __shared__ float gates_s[];
+  float* f_s = gates_s;                              // log forget gate, then f + m_(t-1) - m_t
+  float* i_s = gates_s + (size_t)tile_tokens * heads;  // log input gate, then i - m_t
+  float* m_s = i_s + (size_t)tile_tokens * heads;      // -m_t
   const int row = blockIdx.x;
   const int first = seq_bounds[row], end = seq_bounds[row + 1];
-  const int count = (end - first) * heads;
-  for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
-    const int t = first + idx / heads, h = idx % heads;
-    const float i = cap * tanhf((log_in.at(t, h) + in_bias[h]) / cap);
-    const float z = cap * tanhf((log_forget.at(t, h) + forget_bias[h]) / cap);
-    take[(size_t)t * heads + h] = i;
-    keep[(size_t)t * heads + h] = -softplus_f(-z);
+  float m = 0.f;
+  float* slot = nullptr;
+  if (threadIdx.x < heads) {
+    slot = state + (size_t)seq_seat[row] * heads + threadIdx.x;
+    m = *slot;
   }
-  __syncthreads();
-  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
-    float* slot = state + (size_t)seq_seat[row] * heads + h;
-    float m = *slot;
-    for (int t = first; t < end; ++t) {
-      const size_t at = (size_t)t * heads + h;
-      const float f = keep[at], i = take[at];
-      const float m_new = fmaxf(f + m, i);
-      keep[at] = f + m - m_new;
-      take[at] = i - m_new;
-      floor_out[at] = -m_new;
-      m = m_new;
+  for (int tile = first; tile < end; tile += tile_tokens) {
+    const int count = min(tile_tokens, end - tile) * heads;
+    for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
+      const int t = tile + idx / heads, h = idx % heads;
+      i_s[idx] = cap * tanhf((log_in.at(t, h) + in_bias[h]) / cap);
+      f_s[idx] = -softplus_f(-(cap * tanhf((log_forget.at(t, h) + forget_bias[h]) / cap)));
     }
-    *slot = m;
+    __syncthreads();
+    if (threadIdx.x < heads) {
+      const int h = threadIdx.x;
+#pragma unroll 4
+      for (int at = h; at < count; at += heads) {
+        const float f = f_s[at], i = i_s[at];
+        const float m_new = fmaxf(f + m, i);
+        f_s[at] = f + m - m_new;
+        i_s[at] = i - m_new;
+        m_s[at] = -m_new;
+        m = m_new;
+      }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
+      const size_t at = (size_t)tile * heads + idx;
+      keep[at] = expf(f_s[idx]);
+      take[at] = expf(i_s[idx]);
+      floor_out[at] = expf(m_s[idx]);
+    }
+    __syncthreads();
   }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
-    const size_t at = (size_t)first * heads + idx;
-    keep[at] = expf(keep[at]);
-    take[at] = expf(take[at]);
-    floor_out[at] = expf(floor_out[at]);
-  }
+  if (slot) *slot = m;
 }
 
 // out[t, h, c] = read[t, h, c] / (max(|read[t, h, value_dim]|, floor[t, h]) + 1e-6) for c < value_dim.
@@ -1063,10 +1076,11 @@ extern "C" int distie_exp_gate_scan(const float* log_in, const float* log_forget
   if (num_seqs <= 0) return 0;
   if (heads < 1 || splits < 1 || !(cap > 0.f) || state == nullptr || in_bias == nullptr || forget_bias == nullptr)
     return DISTIE_ERR_ARG;
-  exp_gate_scan_kernel<<<num_seqs, 256, 0, stream>>>(Sliced{log_in, gate_stride, splits, split_stride},
-                                                     Sliced{log_forget, gate_stride, splits, split_stride}, in_bias,
-                                                     forget_bias, cap, state, seq_bounds, seq_seat, heads, keep, take,
-                                                     floor_out);
+  if (heads > 512) return DISTIE_ERR_UNSUPPORTED;
+  const int tile_tokens = heads <= 16 ? 256 : (4096 / heads < 1 ? 1 : 4096 / heads);
+  exp_gate_scan_kernel<<<num_seqs, 512, 3 * (size_t)tile_tokens * heads * sizeof(float), stream>>>(
+      Sliced{log_in, gate_stride, splits, split_stride}, Sliced{log_forget, gate_stride, splits, split_stride}, in_bias,
+      forget_bias, cap, state, seq_bounds, seq_seat, heads, tile_tokens, keep, take, floor_out);
   DISTIE_LAUNCH_CHECK();
   return 0;
 }

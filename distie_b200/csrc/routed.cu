@@ -22,45 +22,71 @@ namespace distie {
 __device__ __forceinline__ float routed_silu(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float routed_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
 
-constexpr int kRouteThreads = 128;
+constexpr int kRouteThreads = 256;
 constexpr int kMaxTop = 32;
 
-// scores_s: `experts` floats of dynamic shared memory.
-template <typename T>
+// TOK tokens a block: their rows wait in shared memory as floats and a warp takes an expert at a time for all of
+// them, so a router row is read once per TOK tokens, in runs of VEC elements a lane.  Then a warp per token picks
+// the `top` largest scores.  Dynamic shared memory: TOK * hidden floats (the rows), then TOK * experts (the scores).
+template <typename T, int TOK, int VEC>
 __global__ void __launch_bounds__(kRouteThreads)
-route_top_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ router, int hidden, int experts, int top,
-                 int* __restrict__ ids, float* __restrict__ weights) {
-  extern __shared__ float scores_s[];
-  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const T* row = x + (size_t)t * x_stride;
-  for (int e = warp; e < experts; e += kRouteThreads / 32) {
-    const T* w = router + (size_t)e * hidden;
-    float dot = 0.f;
-    for (int i = lane; i < hidden; i += 32) dot += to_float(row[i]) * to_float(w[i]);
-    dot = warp_sum(dot);
-    if (lane == 0) scores_s[e] = routed_sigmoid(dot);
+route_top_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ router, int tokens, int hidden, int experts,
+                 int top, int* __restrict__ ids, float* __restrict__ weights) {
+  extern __shared__ __align__(16) float route_s[];
+  float* x_s = route_s;
+  float* scores_s = route_s + (size_t)TOK * hidden;
+  const int t0 = blockIdx.x * TOK, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int live = min(TOK, tokens - t0);
+  for (int idx = threadIdx.x; idx < TOK * hidden; idx += kRouteThreads) {
+    const int r = idx / hidden, k = idx - r * hidden;
+    x_s[idx] = r < live ? to_float(x[(size_t)(t0 + r) * x_stride + k]) : 0.f;
   }
   __syncthreads();
-  if (warp != 0) return;
-  for (int j = 0; j < top; ++j) {
-    float best = -1.f;  // scores lie in [0, 1]; a score taken is set to -2
-    int at = experts;
-    for (int e = lane; e < experts; e += 32) {
-      const float s = scores_s[e];
-      if (s > best) { best = s; at = e; }  // the first of equal scores within a lane: the lower index
+  for (int e = warp; e < experts; e += kRouteThreads / 32) {
+    const T* w = router + (size_t)e * hidden;
+    float dot[TOK];
+#pragma unroll
+    for (int r = 0; r < TOK; ++r) dot[r] = 0.f;
+    for (int k = lane * VEC; k < hidden; k += 32 * VEC) {
+      float wv[VEC];
+      if constexpr (VEC == 8) load8(w + k, wv);
+      else if constexpr (VEC == 4) { const float4 q = load4(w + k); wv[0] = q.x; wv[1] = q.y; wv[2] = q.z; wv[3] = q.w; }
+      else wv[0] = to_float(w[k]);
+#pragma unroll
+      for (int r = 0; r < TOK; ++r)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) dot[r] += x_s[r * hidden + k + i] * wv[i];
     }
 #pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) {
-      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
-      const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
-      if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
+    for (int r = 0; r < TOK; ++r) {
+      const float z = warp_sum(dot[r]);
+      if (lane == 0) scores_s[r * experts + e] = routed_sigmoid(z);
     }
-    if (lane == 0) {
-      ids[(size_t)t * top + j] = at;
-      weights[(size_t)t * top + j] = best;
-      scores_s[at] = -2.f;
+  }
+  __syncthreads();
+  for (int r = warp; r < live; r += kRouteThreads / 32) {
+    float* mine = scores_s + (size_t)r * experts;
+    const size_t t = t0 + r;
+    for (int j = 0; j < top; ++j) {
+      float best = -1.f;  // scores lie in [0, 1]; a score taken is set to -2
+      int at = experts;
+      for (int e = lane; e < experts; e += 32) {
+        const float sc = mine[e];
+        if (sc > best) { best = sc; at = e; }  // the first of equal scores within a lane: the lower index
+      }
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+        const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
+        if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
+      }
+      if (lane == 0) {
+        ids[t * top + j] = at;
+        weights[t * top + j] = best;
+        mine[at] = -2.f;
+      }
+      __syncwarp();
     }
-    __syncwarp();
   }
 }
 
@@ -354,7 +380,7 @@ __global__ void routed_scatter_kernel(const float* __restrict__ y, int* __restri
 // A tile's rows of A (gathered, scaled) wait in shared memory; a warp takes two weight rows at a time (the gate and the up
 // row of one output column, or two neighbouring columns of the down product), every lane a run of VEC elements of K per
 // round, all loads of a round independent of one another; no barrier inside the walk over K.
-constexpr int kRowsR = 8, kRowsWarps = 8, kRowsPairsPerWarp = 2;
+constexpr int kRowsR = 8, kRowsWarps = 8, kRowsPairsPerWarp = 4;
 
 template <typename T, int VEC>
 __device__ __forceinline__ void load_run(const T* p, float (&v)[VEC]) {
@@ -383,11 +409,18 @@ grouped_rows_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__
     scale_s[tid] = plan.scale[slot];
   }
   __syncthreads();
-  for (int idx = tid; idx < rows * K; idx += kRowsWarps * 32) {
-    const int r = idx / K, k = idx - r * K;
-    float v = to_float(a[(size_t)src_s[r] * a_stride + k]);
-    if (scale_in) v *= scale_s[r];
-    a_s[(size_t)r * K + k] = from_float<T>(v);  // the expert reads weight * x in the engine's type
+  for (int r = 0; r < rows; ++r) {  // the expert reads weight * x in the engine's type
+    const T* src = a + (size_t)src_s[r] * a_stride;
+    const float scale = scale_in ? scale_s[r] : 1.f;
+    for (int k = tid * VEC; k < K; k += kRowsWarps * 32 * VEC) {
+      float v[VEC];
+      load_run<T, VEC>(src + k, v);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[i] *= scale;
+      if constexpr (VEC == 8) store8(a_s + (size_t)r * K + k, v);
+      else if constexpr (VEC == 4) store4(a_s + (size_t)r * K + k, make_float4(v[0], v[1], v[2], v[3]));
+      else a_s[(size_t)r * K + k] = from_float<T>(v[0]);
+    }
   }
   __syncthreads();
   const size_t w_rows = SWIGLU ? 2 * (size_t)N : (size_t)N;
@@ -468,16 +501,25 @@ extern "C" int distie_route_top(const void* x, int x_stride, const void* router,
                                 int top, int* ids, float* weights, int dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (hidden < 1 || experts < 1 || top < 1 || top > experts || top > kMaxTop || experts > 8192) return DISTIE_ERR_ARG;
-  const size_t shared = (size_t)experts * sizeof(float);
-  if (dtype == DISTIE_BF16)
-    route_top_kernel<<<tokens, kRouteThreads, shared, stream>>>((const __nv_bfloat16*)x, x_stride,
-                                                               (const __nv_bfloat16*)router, hidden, experts, top, ids,
-                                                               weights);
-  else if (dtype == DISTIE_F32)
-    route_top_kernel<<<tokens, kRouteThreads, shared, stream>>>((const float*)x, x_stride, (const float*)router, hidden,
-                                                               experts, top, ids, weights);
-  else
-    return DISTIE_ERR_UNSUPPORTED;
+  if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
+  const int wide = dtype == DISTIE_BF16 ? 8 : 4;
+  const bool vec = hidden % wide == 0 && ((uintptr_t)router & 15) == 0;
+  const int tok = tokens >= 64 && (size_t)4 * (hidden + experts) * sizeof(float) <= 96 * 1024 ? 4 : 1;
+  const size_t shared = (size_t)tok * (hidden + experts) * sizeof(float);
+  if (shared > 200 * 1024) return DISTIE_ERR_UNSUPPORTED;
+  const unsigned blocks = (unsigned)((tokens + tok - 1) / tok);
+  auto run = [&](auto kernel, auto xp, auto rp) {
+    if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    kernel<<<blocks, kRouteThreads, shared, stream>>>(xp, x_stride, rp, tokens, hidden, experts, top, ids, weights);
+  };
+#define DISTIE_ROUTE(T, VECV)                                                                             \
+  do {                                                                                                    \
+    if (tok == 4) run(route_top_kernel<T, 4, VECV>, (const T*)x, (const T*)router);                       \
+    else run(route_top_kernel<T, 1, VECV>, (const T*)x, (const T*)router);                                \
+  } while (0)
+  if (dtype == DISTIE_BF16) { if (vec) DISTIE_ROUTE(__nv_bfloat16, 8); else DISTIE_ROUTE(__nv_bfloat16, 1); }
+  else { if (vec) DISTIE_ROUTE(float, 4); else DISTIE_ROUTE(float, 1); }
+#undef DISTIE_ROUTE
   DISTIE_LAUNCH_CHECK();
   return 0;
 }
