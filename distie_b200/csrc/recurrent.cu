@@ -786,15 +786,36 @@ exp_gate_scan_kernel(Sliced log_in, Sliced log_forget, const float* __restrict__
     }
     __syncthreads();
     if (threadIdx.x < heads) {
-      const int h = threadIdx.x;
-#pragma unroll 4
-      for (int at = h; at < count; at += heads) {
-        const float f = f_s[at], i = i_s[at];
-        const float m_new = fmaxf(f + m, i);
-        f_s[at] = f + m - m_new;
-        i_s[at] = i - m_new;
-        m_s[at] = -m_new;
-        m = m_new;
+      // Eight tokens at a time: their gates come out of shared memory together, the chain runs in registers, the
+      // results go back together (loads and stores of the same arrays would otherwise wait for one another).
+      const int h = threadIdx.x, steps = count / heads;
+      for (int base = 0; base < steps; base += 8) {
+        float f[8], i[8], m_out[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int at = (min(base + u, steps - 1)) * heads + h;
+          f[u] = f_s[at];
+          i[u] = i_s[at];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (base + u < steps) {
+            const float m_new = fmaxf(f[u] + m, i[u]);
+            f[u] = f[u] + m - m_new;
+            i[u] = i[u] - m_new;
+            m_out[u] = -m_new;
+            m = m_new;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (base + u < steps) {
+            const int at = (base + u) * heads + h;
+            f_s[at] = f[u];
+            i_s[at] = i[u];
+            m_s[at] = m_out[u];
+          }
+        }
       }
     }
     __syncthreads();

@@ -37,9 +37,21 @@ route_top_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
   float* scores_s = route_s + (size_t)TOK * hidden;
   const int t0 = blockIdx.x * TOK, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int live = min(TOK, tokens - t0);
-  for (int idx = threadIdx.x; idx < TOK * hidden; idx += kRouteThreads) {
-    const int r = idx / hidden, k = idx - r * hidden;
-    x_s[idx] = r < live ? to_float(x[(size_t)(t0 + r) * x_stride + k]) : 0.f;
+  for (int r = 0; r < TOK; ++r) {
+    const T* src = x + (size_t)(t0 + min(r, live - 1)) * x_stride;
+    float* dst = x_s + (size_t)r * hidden;
+    if (VEC > 1 && x_stride % VEC == 0 && ((uintptr_t)x & 15) == 0) {
+      for (int k = threadIdx.x * VEC; k < hidden; k += kRouteThreads * VEC) {
+        float v[VEC];
+        if constexpr (VEC == 8) load8(src + k, v);
+        else if constexpr (VEC == 4) { const float4 q = load4(src + k); v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
+        else v[0] = to_float(src[k]);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) dst[k + i] = v[i];
+      }
+    } else {
+      for (int k = threadIdx.x; k < hidden; k += kRouteThreads) dst[k] = to_float(src[k]);
+    }
   }
   __syncthreads();
   for (int e = warp; e < experts; e += kRouteThreads / 32) {
@@ -53,9 +65,17 @@ route_top_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
       else if constexpr (VEC == 4) { const float4 q = load4(w + k); wv[0] = q.x; wv[1] = q.y; wv[2] = q.z; wv[3] = q.w; }
       else wv[0] = to_float(w[k]);
 #pragma unroll
-      for (int r = 0; r < TOK; ++r)
+      for (int r = 0; r < TOK; ++r) {
+        if constexpr (VEC >= 4) {  // (hidden and k are multiples of VEC: the runs are 16-byte aligned)
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) dot[r] += x_s[r * hidden + k + i] * wv[i];
+          for (int i = 0; i < VEC; i += 4) {
+            const float4 q = *reinterpret_cast<const float4*>(x_s + (size_t)r * hidden + k + i);
+            dot[r] += (q.x * wv[i] + q.y * wv[i + 1]) + (q.z * wv[i + 2] + q.w * wv[i + 3]);
+          }
+        } else {
+          dot[r] += x_s[r * hidden + k] * wv[0];
+        }
+      }
     }
 #pragma unroll
     for (int r = 0; r < TOK; ++r) {
@@ -380,7 +400,7 @@ __global__ void routed_scatter_kernel(const float* __restrict__ y, int* __restri
 // A tile's rows of A (gathered, scaled) wait in shared memory; a warp takes two weight rows at a time (the gate and the up
 // row of one output column, or two neighbouring columns of the down product), every lane a run of VEC elements of K per
 // round, all loads of a round independent of one another; no barrier inside the walk over K.
-constexpr int kRowsR = 8, kRowsWarps = 8, kRowsPairsPerWarp = 4;
+constexpr int kRowsR = 8, kRowsWarps = 8, kRowsPairsPerWarp = 2;
 
 template <typename T, int VEC>
 __device__ __forceinline__ void load_run(const T* p, float (&v)[VEC]) {
@@ -437,17 +457,32 @@ grouped_rows_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__
     float acc0[kRowsR], acc1[kRowsR];
 #pragma unroll
     for (int r = 0; r < kRowsR; ++r) acc0[r] = acc1[r] = 0.f;
-    for (int k = lane * VEC; k < K; k += 32 * VEC) {
-      float x0[VEC], x1[VEC];
-      load_run<T, VEC>(w0 + k, x0);
-      load_run<T, VEC>(w1 + k, x1);
+    // Three rounds of K at a time: their six runs of the two weight rows are requested before any is used.
+    constexpr int AHEAD = 3;
+    for (int k0 = lane * VEC; k0 < K; k0 += AHEAD * 32 * VEC) {
+      float x0[AHEAD][VEC], x1[AHEAD][VEC];
 #pragma unroll
-      for (int r = 0; r < kRowsR; ++r) {
-        if (r < rows) {
-          float av[VEC];
-          load_run<T, VEC>(a_s + (size_t)r * K + k, av);
+      for (int u = 0; u < AHEAD; ++u) {
+        const int k = k0 + u * 32 * VEC;
+        if (k < K) {
+          load_run<T, VEC>(w0 + k, x0[u]);
+          load_run<T, VEC>(w1 + k, x1[u]);
+        } else {
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) { acc0[r] += av[i] * x0[i]; acc1[r] += av[i] * x1[i]; }
+          for (int i = 0; i < VEC; ++i) x0[u][i] = x1[u][i] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < AHEAD; ++u) {
+        const int k = min(k0 + u * 32 * VEC, K - VEC);  // (a round past the end multiplies zeros)
+#pragma unroll
+        for (int r = 0; r < kRowsR; ++r) {
+          if (r < rows) {
+            float av[VEC];
+            load_run<T, VEC>(a_s + (size_t)r * K + k, av);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) { acc0[r] += av[i] * x0[u][i]; acc1[r] += av[i] * x1[u][i]; }
+          }
         }
       }
     }
