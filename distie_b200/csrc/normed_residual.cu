@@ -7,7 +7,7 @@
 //  * qk_rope_norm_write: from the float32 projection [q | k] (a matrix or the slices of a split product) plus
 //    bias: the key as projected is stored as the value; q and k are rotated over the first `rotary_dim`
 //    elements of each head (angles pos * inv_freq in float32), then each head is divided by its root mean
-//    square; k goes to its page and q to its buffer.  One block per (token, head).
+//    square; k goes to its page and q to its buffer.  One block per token, a warp per head.
 //
 // All arithmetic is float32; T is the type of what is stored for the next product or in the cache.
 #include "common.cuh"
@@ -133,8 +133,12 @@ struct SlicedRows {
   }
 };
 
+constexpr int kRopeWarps = 8;
+
+// A block per token, a warp per head (in turns): the head waits in the warp's own piece of shared memory between
+// the load, the rotation of its pairs and the stores.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kRopeWarps * 32)
 qk_rope_norm_write_kernel(SlicedRows qk, const float* __restrict__ bias, T* __restrict__ q_out, int q_out_stride,
                           const int* __restrict__ positions, const int* __restrict__ token_seq,
                           const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
@@ -142,52 +146,54 @@ qk_rope_norm_write_kernel(SlicedRows qk, const float* __restrict__ bias, T* __re
                           T* __restrict__ v_cache, int num_heads, int num_kv_heads, int head_dim, int rotary_dim,
                           int interleaved, int page_size, int num_pages, int write, int normed, float norm_eps,
                           int* __restrict__ error) {
-  extern __shared__ __align__(16) float head_s[];  // head_dim floats: the head as projected, then rotated
-  __shared__ float scratch[32];
-  const int t = blockIdx.x, head = blockIdx.y;
-  const bool is_key = head >= num_heads;
-  if (is_key && !write) return;
+  extern __shared__ __align__(16) float heads_s[];  // kRopeWarps pieces of head_dim floats
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* head_s = heads_s + (size_t)warp * head_dim;
   const int pos = positions[t];
-  const int column0 = head * head_dim;
-  for (int e = threadIdx.x; e < head_dim; e += blockDim.x)
-    head_s[e] = qk.at(t, column0 + e) + (bias ? bias[column0 + e] : 0.f);
-  __syncthreads();
-  size_t cache_row = 0;
-  bool store = !is_key;
-  if (is_key) {
+  const int half = rotary_dim / 2;
+  int page = -1;
+  if (write) {
     const int seat = seq_seat[token_seq[t]];
     const int column = pos / page_size;
-    const int page = column < table_width ? block_table[(size_t)seat * table_width + column] : -1;
+    page = column < table_width ? block_table[(size_t)seat * table_width + column] : -1;
     if (page < 0 || page >= num_pages) {
       if (threadIdx.x == 0 && error) atomicExch(error, 2);
-    } else {
-      store = true;
-      cache_row = (((size_t)page * num_kv_heads + (head - num_heads)) * page_size + pos % page_size) * head_dim;
-      for (int e = threadIdx.x; e < head_dim; e += blockDim.x) v_cache[cache_row + e] = from_float<T>(head_s[e]);
+      page = -1;
     }
   }
-  // Rotation: every pair is read and written by one thread.
-  const int half = rotary_dim / 2;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
-    float sn, cs;
-    sincosf((float)pos * inv_freq[i], &sn, &cs);
-    sn *= factor;
-    cs *= factor;
-    const float u = head_s[a], v = head_s[b];
-    const float ru = u * cs - v * sn, rv = v * cs + u * sn;
-    head_s[a] = ru;
-    head_s[b] = rv;
-    ss += ru * ru + rv * rv;
+  const int heads_here = num_heads + (write ? num_kv_heads : 0);
+  for (int head = warp; head < heads_here; head += kRopeWarps) {
+    const bool is_key = head >= num_heads;
+    const int column0 = head * head_dim;
+    for (int e = lane; e < head_dim; e += 32) head_s[e] = qk.at(t, column0 + e) + (bias ? bias[column0 + e] : 0.f);
+    __syncwarp();
+    size_t cache_row = 0;
+    if (is_key && page >= 0) {
+      cache_row = (((size_t)page * num_kv_heads + (head - num_heads)) * page_size + pos % page_size) * head_dim;
+      for (int e = lane; e < head_dim; e += 32) v_cache[cache_row + e] = from_float<T>(head_s[e]);
+    }
+    float ss = 0.f;
+    for (int i = lane; i < half; i += 32) {  // every pair is read and written by one lane
+      const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+      float sn, cs;
+      sincosf((float)pos * inv_freq[i], &sn, &cs);
+      sn *= factor;
+      cs *= factor;
+      const float u = head_s[a], v = head_s[b];
+      const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+      head_s[a] = ru;
+      head_s[b] = rv;
+      ss += ru * ru + rv * rv;
+    }
+    for (int e = rotary_dim + lane; e < head_dim; e += 32) ss += head_s[e] * head_s[e];
+    __syncwarp();
+    const float unit = normed ? rsqrtf(warp_sum(ss) / (float)head_dim + norm_eps) : 1.f;
+    if (!is_key || page >= 0) {
+      T* dst = is_key ? k_cache + cache_row : q_out + (size_t)t * q_out_stride + column0;
+      for (int e = lane; e < head_dim; e += 32) dst[e] = from_float<T>(head_s[e] * unit);
+    }
+    __syncwarp();  // before the next head overwrites the piece
   }
-  for (int e = rotary_dim + threadIdx.x; e < head_dim; e += blockDim.x) ss += head_s[e] * head_s[e];
-  float unit = 1.f;
-  if (normed) unit = rsqrtf(block_sum(ss, scratch) / (float)head_dim + norm_eps);
-  else __syncthreads();
-  if (!store) return;
-  T* dst = is_key ? k_cache + cache_row : q_out + (size_t)t * q_out_stride + column0;
-  for (int e = threadIdx.x; e < head_dim; e += blockDim.x) dst[e] = from_float<T>(head_s[e] * unit);
 }
 
 }  // namespace distie
@@ -261,9 +267,9 @@ extern "C" int distie_qk_rope_norm_write(const float* qk, int qk_stride, int spl
       (rotary_dim & 1) || (rotary_dim > 0 && inv_freq == nullptr) || splits < 1 || page_size < 1 ||
       num_heads + num_kv_heads > 65535 || (write && (k_cache == nullptr || v_cache == nullptr)))
     return DISTIE_ERR_ARG;
-  const dim3 grid(tokens, num_heads + num_kv_heads);
-  const int threads = head_dim >= 256 ? 256 : (head_dim >= 128 ? 128 : 64);
-  const size_t shared = (size_t)head_dim * sizeof(float);
+  const dim3 grid(tokens);
+  const int threads = kRopeWarps * 32;
+  const size_t shared = (size_t)kRopeWarps * head_dim * sizeof(float);
   const SlicedRows rows{qk, qk_stride, splits, split_stride};
   if (dtype == DISTIE_BF16)
     qk_rope_norm_write_kernel<<<grid, threads, shared, stream>>>(

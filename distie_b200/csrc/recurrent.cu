@@ -758,7 +758,7 @@ __global__ void activation_kernel(Sliced x, float* __restrict__ out, int tokens,
 // by token (a thread per head: an addition and a maximum per token on the chain, its operands already on the chip),
 // then the exponentials side by side and out.  The walk is the plain sequence of operations whatever the tile or the
 // cutting of the prompt, so its results depend on neither.
-// gates_s: 3 * tile_tokens * heads floats of dynamic shared memory.
+// gates_s: 5 * tile_tokens * heads floats of dynamic shared memory.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(512)
 exp_gate_scan_kernel(Sliced log_in, Sliced log_forget, const float* __restrict__ in_bias,
@@ -766,9 +766,9 @@ exp_gate_scan_kernel(Sliced log_in, Sliced log_forget, const float* __restrict__
                      const int* __restrict__ seq_bounds, const int* __restrict__ seq_seat, int heads, int tile_tokens,
                      float* __restrict__ keep, float* __restrict__ take, float* __restrict__ floor_out) {
   extern __shared__ float gates_s[];
-  float* f_s = gates_s;                              // log forget gate, then f + m_(t-1) - m_t
-  float* i_s = gates_s + (size_t)tile_tokens * heads;  // log input gate, then i - m_t
-  float* m_s = i_s + (size_t)tile_tokens * heads;      // -m_t
+  float* f_s = gates_s;                                // log forget gate
+  float* i_s = gates_s + (size_t)tile_tokens * heads;  // log input gate
+  float* m_s = i_s + (size_t)tile_tokens * heads;      // three arrays: f + m_(t-1) - m_t, i - m_t, -m_t
   const int row = blockIdx.x;
   const int first = seq_bounds[row], end = seq_bounds[row + 1];
   float m = 0.f;
@@ -786,44 +786,29 @@ exp_gate_scan_kernel(Sliced log_in, Sliced log_forget, const float* __restrict__
     }
     __syncthreads();
     if (threadIdx.x < heads) {
-      // Eight tokens at a time: their gates come out of shared memory together, the chain runs in registers, the
-      // results go back together (loads and stores of the same arrays would otherwise wait for one another).
-      const int h = threadIdx.x, steps = count / heads;
-      for (int base = 0; base < steps; base += 8) {
-        float f[8], i[8], m_out[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int at = (min(base + u, steps - 1)) * heads + h;
-          f[u] = f_s[at];
-          i[u] = i_s[at];
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          if (base + u < steps) {
-            const float m_new = fmaxf(f[u] + m, i[u]);
-            f[u] = f[u] + m - m_new;
-            i[u] = i[u] - m_new;
-            m_out[u] = -m_new;
-            m = m_new;
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          if (base + u < steps) {
-            const int at = (base + u) * heads + h;
-            f_s[at] = f[u];
-            i_s[at] = i[u];
-            m_s[at] = m_out[u];
-          }
-        }
+      // The chain reads the gates from two arrays and writes its results to three others, so that the loads of
+      // later tokens need not wait for the stores of earlier ones.
+      const float* __restrict__ f_in = f_s;
+      const float* __restrict__ i_in = i_s;
+      float* __restrict__ keep_o = m_s;
+      float* __restrict__ take_o = m_s + (size_t)tile_tokens * heads;
+      float* __restrict__ floor_o = m_s + 2 * (size_t)tile_tokens * heads;
+#pragma unroll 8
+      for (int at = threadIdx.x; at < count; at += heads) {
+        const float f = f_in[at], i = i_in[at];
+        const float m_new = fmaxf(f + m, i);
+        keep_o[at] = f + m - m_new;
+        take_o[at] = i - m_new;
+        floor_o[at] = -m_new;
+        m = m_new;
       }
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
       const size_t at = (size_t)tile * heads + idx;
-      keep[at] = expf(f_s[idx]);
-      take[at] = expf(i_s[idx]);
-      floor_out[at] = expf(m_s[idx]);
+      keep[at] = expf(m_s[idx]);
+      take[at] = expf(m_s[(size_t)tile_tokens * heads + idx]);
+      floor_out[at] = expf(m_s[2 * (size_t)tile_tokens * heads + idx]);
     }
     __syncthreads();
   }
@@ -1098,8 +1083,8 @@ extern "C" int distie_exp_gate_scan(const float* log_in, const float* log_forget
   if (heads < 1 || splits < 1 || !(cap > 0.f) || state == nullptr || in_bias == nullptr || forget_bias == nullptr)
     return DISTIE_ERR_ARG;
   if (heads > 512) return DISTIE_ERR_UNSUPPORTED;
-  const int tile_tokens = heads <= 16 ? 256 : (4096 / heads < 1 ? 1 : 4096 / heads);
-  exp_gate_scan_kernel<<<num_seqs, 512, 3 * (size_t)tile_tokens * heads * sizeof(float), stream>>>(
+  const int tile_tokens = heads <= 16 ? 128 : (2048 / heads < 1 ? 1 : 2048 / heads);
+  exp_gate_scan_kernel<<<num_seqs, 512, 5 * (size_t)tile_tokens * heads * sizeof(float), stream>>>(
       Sliced{log_in, gate_stride, splits, split_stride}, Sliced{log_forget, gate_stride, splits, split_stride}, in_bias,
       forget_bias, cap, state, seq_bounds, seq_seat, heads, tile_tokens, keep, take, floor_out);
   DISTIE_LAUNCH_CHECK();

@@ -400,7 +400,7 @@ __global__ void routed_scatter_kernel(const float* __restrict__ y, int* __restri
 // A tile's rows of A (gathered, scaled) wait in shared memory; a warp takes two weight rows at a time (the gate and the up
 // row of one output column, or two neighbouring columns of the down product), every lane a run of VEC elements of K per
 // round, all loads of a round independent of one another; no barrier inside the walk over K.
-constexpr int kRowsR = 8, kRowsWarps = 8, kRowsPairsPerWarp = 2;
+constexpr int kRowsR = 8, kRowsWarps = 8;
 
 template <typename T, int VEC>
 __device__ __forceinline__ void load_run(const T* p, float (&v)[VEC]) {
@@ -411,7 +411,7 @@ __device__ __forceinline__ void load_run(const T* p, float (&v)[VEC]) {
 
 template <typename T, bool SWIGLU, int VEC>
 __global__ void __launch_bounds__(kRowsWarps * 32)
-grouped_rows_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ w, int* __restrict__ plan_base, int pairs,
+grouped_rows_kernel(int rounds, const T* __restrict__ a, int a_stride, const T* __restrict__ w, int* __restrict__ plan_base, int pairs,
                     int experts, T* __restrict__ out, float* __restrict__ out32, int N, int K, int gather, int scale_in,
                     int scale_out) {
   extern __shared__ __align__(16) unsigned char rows_raw[];
@@ -446,9 +446,9 @@ grouped_rows_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__
   const size_t w_rows = SWIGLU ? 2 * (size_t)N : (size_t)N;
   const T* w_e = w + (size_t)expert * w_rows * K;
   constexpr int COLS = SWIGLU ? 1 : 2;  // output columns a warp finishes per round
-  const int col0 = (blockIdx.y * kRowsWarps * kRowsPairsPerWarp + warp * kRowsPairsPerWarp) * COLS;
+  const int col0 = (blockIdx.y * kRowsWarps * rounds + warp * rounds) * COLS;  // `rounds` pairs of weight rows a warp
 #pragma unroll 1
-  for (int round = 0; round < kRowsPairsPerWarp; ++round) {
+  for (int round = 0; round < rounds; ++round) {
     const int n = col0 + round * COLS;
     if (n >= N) break;
     const bool second = SWIGLU || n + 1 < N;
@@ -514,11 +514,13 @@ static int launch_grouped_rows(const T* a, int a_stride, const T* w, int* plan, 
   constexpr int WIDE = sizeof(T) == 2 ? 8 : 4;
   const bool vec = K % WIDE == 0 && a_stride % WIDE == 0 && (((uintptr_t)a | (uintptr_t)w) & 15) == 0;
   const size_t shared = (size_t)kRowsR * K * sizeof(T);
-  const int per_block = kRowsWarps * kRowsPairsPerWarp * (SWIGLU ? 1 : 2);
+  // Pairs of weight rows a warp takes in turn: fewer where the product has few columns, so that the grid stays large.
+  const int rounds = (long long)N * (SWIGLU ? 2 : 1) >= 4096 ? 4 : 2;
+  const int per_block = kRowsWarps * rounds * (SWIGLU ? 1 : 2);
   const dim3 grid(max_tiles, (N + per_block - 1) / per_block);
   auto run = [&](auto kernel) {
     if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-    kernel<<<grid, kRowsWarps * 32, shared, stream>>>(a, a_stride, w, plan, pairs, experts, out, out32, N, K, gather, scale_in,
+    kernel<<<grid, kRowsWarps * 32, shared, stream>>>(rounds, a, a_stride, w, plan, pairs, experts, out, out32, N, K, gather, scale_in,
                                                      scale_out);
   };
   if (vec) run(grouped_rows_kernel<T, SWIGLU, WIDE>);
