@@ -162,7 +162,7 @@ qk_rope_norm_write_kernel(SlicedRows qk, const float* __restrict__ bias, T* __re
     }
   }
   const int heads_here = num_heads + (write ? num_kv_heads : 0);
-  for (int head = warp; head < heads_here; head += kRopeWarps) {
+  for (int head = blockIdx.y * kRopeWarps + warp; head < heads_here; head += gridDim.y * kRopeWarps) {
     const bool is_key = head >= num_heads;
     const int column0 = head * head_dim;
     for (int e = lane; e < head_dim; e += 32) head_s[e] = qk.at(t, column0 + e) + (bias ? bias[column0 + e] : 0.f);
@@ -267,7 +267,8 @@ extern "C" int distie_qk_rope_norm_write(const float* qk, int qk_stride, int spl
       (rotary_dim & 1) || (rotary_dim > 0 && inv_freq == nullptr) || splits < 1 || page_size < 1 ||
       num_heads + num_kv_heads > 65535 || (write && (k_cache == nullptr || v_cache == nullptr)))
     return DISTIE_ERR_ARG;
-  const dim3 grid(tokens);
+  // Few tokens: the heads of a token spread over several blocks, so that the step fills more of the machine.
+  const dim3 grid(tokens, tokens < 512 ? (num_heads + num_kv_heads + kRopeWarps - 1) / kRopeWarps : 1);
   const int threads = kRopeWarps * 32;
   const size_t shared = (size_t)kRopeWarps * head_dim * sizeof(float);
   const SlicedRows rows{qk, qk_stride, splits, split_stride};

@@ -751,24 +751,39 @@ __global__ void activation_kernel(Sliced x, float* __restrict__ out, int tokens,
 }
 
 // ---------------------------------------------------------------------------
-// Exponential gates under a running maximum, one block per request of the step:
+// Exponential gates under a running maximum:
 //   i = cap tanh((x_i + b_i) / cap);  f = logsigmoid(cap tanh((x_f + b_f) / cap));  m_t = max(f_t + m_(t-1), i_t)
 //   keep = exp(f + m_(t-1) - m_t);  take = exp(i - m_t);  floor = exp(-m_t);  m lives in state[seat, head].
-// The request's tokens go through shared memory in tiles: the gates of a tile side by side, then the maximum token
-// by token (a thread per head: an addition and a maximum per token on the chain, its operands already on the chip),
-// then the exponentials side by side and out.  The walk is the plain sequence of operations whatever the tile or the
-// cutting of the prompt, so its results depend on neither.
-// gates_s: 5 * tile_tokens * heads floats of dynamic shared memory.
+// Three kernels.  The gates of all tokens side by side over the whole machine (f into `keep`, i into `take`).  Then
+// a block per request walks its tokens: a tile of gates comes into shared memory, a thread per head runs the chain
+// (an addition and a maximum per token, its operands on the chip; it reads two arrays and writes three others, so
+// that later loads need not wait for earlier stores), and the exponents go back out.  Then the exponentials side
+// by side.  The walk is the plain sequence of operations whatever the tile or the cutting of the prompt.
 // ---------------------------------------------------------------------------
+__global__ void exp_gates_kernel(Sliced log_in, Sliced log_forget, const float* __restrict__ in_bias,
+                                 const float* __restrict__ forget_bias, float cap, int tokens, int heads,
+                                 float* __restrict__ keep, float* __restrict__ take) {
+  const size_t total = (size_t)tokens * heads;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / heads;
+    const int h = (int)(idx % heads);
+    take[idx] = cap * tanhf((log_in.at(t, h) + in_bias[h]) / cap);
+    keep[idx] = -softplus_f(-(cap * tanhf((log_forget.at(t, h) + forget_bias[h]) / cap)));
+  }
+}
+
+// gates_s: 5 * tile_tokens * heads floats of dynamic shared memory.
 __global__ void __launch_bounds__(512)
-exp_gate_scan_kernel(Sliced log_in, Sliced log_forget, const float* __restrict__ in_bias,
-                     const float* __restrict__ forget_bias, float cap, float* __restrict__ state,
-                     const int* __restrict__ seq_bounds, const int* __restrict__ seq_seat, int heads, int tile_tokens,
-                     float* __restrict__ keep, float* __restrict__ take, float* __restrict__ floor_out) {
+exp_gate_scan_kernel(float* __restrict__ state, const int* __restrict__ seq_bounds, const int* __restrict__ seq_seat,
+                     int heads, int tile_tokens, float* __restrict__ keep, float* __restrict__ take,
+                     float* __restrict__ floor_out) {
   extern __shared__ float gates_s[];
-  float* f_s = gates_s;                                // log forget gate
-  float* i_s = gates_s + (size_t)tile_tokens * heads;  // log input gate
-  float* m_s = i_s + (size_t)tile_tokens * heads;      // three arrays: f + m_(t-1) - m_t, i - m_t, -m_t
+  const size_t plane = (size_t)tile_tokens * heads;
+  const float* __restrict__ f_in = gates_s;
+  const float* __restrict__ i_in = gates_s + plane;
+  float* __restrict__ keep_o = gates_s + 2 * plane;
+  float* __restrict__ take_o = gates_s + 3 * plane;
+  float* __restrict__ floor_o = gates_s + 4 * plane;
   const int row = blockIdx.x;
   const int first = seq_bounds[row], end = seq_bounds[row + 1];
   float m = 0.f;
@@ -779,20 +794,13 @@ exp_gate_scan_kernel(Sliced log_in, Sliced log_forget, const float* __restrict__
   }
   for (int tile = first; tile < end; tile += tile_tokens) {
     const int count = min(tile_tokens, end - tile) * heads;
+    const size_t base = (size_t)tile * heads;
     for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
-      const int t = tile + idx / heads, h = idx % heads;
-      i_s[idx] = cap * tanhf((log_in.at(t, h) + in_bias[h]) / cap);
-      f_s[idx] = -softplus_f(-(cap * tanhf((log_forget.at(t, h) + forget_bias[h]) / cap)));
+      gates_s[idx] = keep[base + idx];
+      gates_s[plane + idx] = take[base + idx];
     }
     __syncthreads();
     if (threadIdx.x < heads) {
-      // The chain reads the gates from two arrays and writes its results to three others, so that the loads of
-      // later tokens need not wait for the stores of earlier ones.
-      const float* __restrict__ f_in = f_s;
-      const float* __restrict__ i_in = i_s;
-      float* __restrict__ keep_o = m_s;
-      float* __restrict__ take_o = m_s + (size_t)tile_tokens * heads;
-      float* __restrict__ floor_o = m_s + 2 * (size_t)tile_tokens * heads;
 #pragma unroll 8
       for (int at = threadIdx.x; at < count; at += heads) {
         const float f = f_in[at], i = i_in[at];
@@ -805,14 +813,21 @@ exp_gate_scan_kernel(Sliced log_in, Sliced log_forget, const float* __restrict__
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
-      const size_t at = (size_t)tile * heads + idx;
-      keep[at] = expf(m_s[idx]);
-      take[at] = expf(m_s[(size_t)tile_tokens * heads + idx]);
-      floor_out[at] = expf(m_s[2 * (size_t)tile_tokens * heads + idx]);
+      keep[base + idx] = keep_o[idx];
+      take[base + idx] = take_o[idx];
+      floor_out[base + idx] = floor_o[idx];
     }
     __syncthreads();
   }
   if (slot) *slot = m;
+}
+
+__global__ void exp_three_kernel(float* __restrict__ a, float* __restrict__ b, float* __restrict__ c, size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    a[idx] = expf(a[idx]);
+    b[idx] = expf(b[idx]);
+    c[idx] = expf(c[idx]);
+  }
 }
 
 // out[t, h, c] = read[t, h, c] / (max(|read[t, h, value_dim]|, floor[t, h]) + 1e-6) for c < value_dim.
@@ -1077,16 +1092,23 @@ extern "C" int distie_activation(const float* x, int x_stride, int splits, long 
 // contiguous; state [seats, heads].
 extern "C" int distie_exp_gate_scan(const float* log_in, const float* log_forget, int gate_stride, int splits,
                                     long long split_stride, const float* in_bias, const float* forget_bias, float cap,
-                                    float* state, const int* seq_bounds, const int* seq_seat, int num_seqs, int heads,
-                                    float* keep, float* take, float* floor_out, cudaStream_t stream) {
+                                    float* state, const int* seq_bounds, const int* seq_seat, int num_seqs, int tokens,
+                                    int heads, float* keep, float* take, float* floor_out, cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
   if (heads < 1 || splits < 1 || !(cap > 0.f) || state == nullptr || in_bias == nullptr || forget_bias == nullptr)
     return DISTIE_ERR_ARG;
-  if (heads > 512) return DISTIE_ERR_UNSUPPORTED;
+  if (heads > 512 || tokens < 1) return DISTIE_ERR_UNSUPPORTED;
+  const size_t total = (size_t)tokens * heads;
+  const unsigned blocks = (unsigned)((total + 255) / 256 > 148 * 8 ? 148 * 8 : (total + 255) / 256);
+  exp_gates_kernel<<<blocks, 256, 0, stream>>>(Sliced{log_in, gate_stride, splits, split_stride},
+                                              Sliced{log_forget, gate_stride, splits, split_stride}, in_bias, forget_bias,
+                                              cap, tokens, heads, keep, take);
+  DISTIE_LAUNCH_CHECK();
   const int tile_tokens = heads <= 16 ? 128 : (2048 / heads < 1 ? 1 : 2048 / heads);
   exp_gate_scan_kernel<<<num_seqs, 512, 5 * (size_t)tile_tokens * heads * sizeof(float), stream>>>(
-      Sliced{log_in, gate_stride, splits, split_stride}, Sliced{log_forget, gate_stride, splits, split_stride}, in_bias,
-      forget_bias, cap, state, seq_bounds, seq_seat, heads, tile_tokens, keep, take, floor_out);
+      state, seq_bounds, seq_seat, heads, tile_tokens, keep, take, floor_out);
+  DISTIE_LAUNCH_CHECK();
+  exp_three_kernel<<<blocks, 256, 0, stream>>>(keep, take, floor_out, total);
   DISTIE_LAUNCH_CHECK();
   return 0;
 }

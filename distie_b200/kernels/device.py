@@ -677,12 +677,12 @@ class DeviceKernels(KernelSet):
         check(
             function("distie_exp_gate_scan")(
                 in_ptr, forget_ptr, stride, splits, split_stride, in_bias.data_ptr(), forget_bias.data_ptr(), float(cap),
-                state.data_ptr(), self._seq_index(step)[1].data_ptr(), step.seq_seat.data_ptr(), step.num_seqs, heads,
-                gates[0].data_ptr(), gates[1].data_ptr(), gates[2].data_ptr(), self._stream(),
+                state.data_ptr(), self._seq_index(step)[1].data_ptr(), step.seq_seat.data_ptr(), step.num_seqs,
+                step.num_tokens, heads, gates[0].data_ptr(), gates[1].data_ptr(), gates[2].data_ptr(), self._stream(),
             ),
             "exp_gate_scan",
         )
-        self._ran("exp_gate_scan")
+        self._ran("exp_gate_scan", 3)
         return gates[0], gates[1], gates[2]
 
     def stabilized_readout(self, read, floor, heads, value_dim):

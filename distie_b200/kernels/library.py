@@ -58,7 +58,7 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
         "state", [I, P, I, P, I, P, I, P, I, P, I, I, L, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, P]
     ),
     "distie_activation": ("state", [P, I, I, L, P, I, I, I, F, I, P]),
-    "distie_exp_gate_scan": ("state", [P, P, I, I, L, P, P, F, P, P, P, I, I, P, P, P, P]),
+    "distie_exp_gate_scan": ("state", [P, P, I, I, L, P, P, F, P, P, P, I, I, I, P, P, P, P]),
     "distie_stabilized_readout": ("state", [P, I, P, P, I, I, I, P]),
     "distie_route_top": ("routed", [P, I, P, I, I, I, I, P, P, I, P]),
     "distie_routed_tile": ("routed", [I, I, I, I, I]),
