@@ -110,6 +110,39 @@ route_top_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
   }
 }
 
+// The choice alone, from float32 logits [tokens, experts] that a product left: a warp per token.
+__global__ void __launch_bounds__(kRouteThreads)
+route_pick_kernel(const float* __restrict__ logits, int logit_stride, int tokens, int experts, int top,
+                  int* __restrict__ ids, float* __restrict__ weights) {
+  extern __shared__ float pick_s[];  // a row of scores per warp
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (kRouteThreads / 32) + warp;
+  if (t >= tokens) return;
+  float* mine = pick_s + (size_t)warp * experts;
+  for (int e = lane; e < experts; e += 32) mine[e] = routed_sigmoid(logits[(size_t)t * logit_stride + e]);
+  __syncwarp();
+  for (int j = 0; j < top; ++j) {
+    float best = -1.f;
+    int at = experts;
+    for (int e = lane; e < experts; e += 32) {
+      const float sc = mine[e];
+      if (sc > best) { best = sc; at = e; }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+      const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
+      if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
+    }
+    if (lane == 0) {
+      ids[(size_t)t * top + j] = at;
+      weights[(size_t)t * top + j] = best;
+      mine[at] = -2.f;
+    }
+    __syncwarp();
+  }
+}
+
 // plan layout (int32): [0] number of tiles; [1 .. 1 + experts] offsets of the experts' slots; then
 // tile_expert[max_tiles], tile_first[max_tiles], tile_rows[max_tiles]; then per slot source[pairs], dest[pairs];
 // scale[pairs] (float bits).  max_tiles = pairs / tile + experts (rounded up).
@@ -672,6 +705,20 @@ extern "C" int distie_routed_scatter(const float* y, int* plan, int pairs, int e
                                      int scale_out, cudaStream_t stream) {
   if (pairs <= 0) return 0;
   routed_scatter_kernel<<<pairs, 256, 0, stream>>>(y, plan, pairs, experts, tile, out, hidden, scale_out);
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+// ids and weights from float32 logits [tokens, experts] (row stride logit_stride): see route_pick_kernel.
+extern "C" int distie_route_pick(const float* logits, int logit_stride, int tokens, int experts, int top, int* ids,
+                                 float* weights, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (experts < 1 || top < 1 || top > experts || top > kMaxTop || experts > 4096) return DISTIE_ERR_ARG;
+  const int warps = kRouteThreads / 32;
+  const size_t shared = (size_t)warps * experts * sizeof(float);
+  if (shared > 48 * 1024) cudaFuncSetAttribute(route_pick_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+  route_pick_kernel<<<(tokens + warps - 1) / warps, kRouteThreads, shared, stream>>>(logits, logit_stride, tokens, experts,
+                                                                                    top, ids, weights);
   DISTIE_LAUNCH_CHECK();
   return 0;
 }

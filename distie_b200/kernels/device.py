@@ -709,6 +709,15 @@ class DeviceKernels(KernelSet):
         tokens, experts = x.shape[0], router.shape[0]
         ids = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
         weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
+        if self._tensor_core(x, router):
+            # Prompt portions in bfloat16: the logits are a product on the tcgen05 tile kernel (float32 accumulators,
+            # stored as float32), and a small kernel picks from them.
+            logits = torch.empty((tokens, experts), dtype=torch.float32, device=x.device)
+            self._gemm_tcgen05(x, router, logits, 1)
+            check(function("distie_route_pick")(logits.data_ptr(), logits.stride(0), tokens, experts, top, ids.data_ptr(),
+                                                weights.data_ptr(), self._stream()), "route_pick")
+            self._ran("route_top")
+            return ids, weights
         check(
             function("distie_route_top")(x.data_ptr(), x.stride(0), router.data_ptr(), tokens, x.shape[1], experts, top,
                                          ids.data_ptr(), weights.data_ptr(), _CODE[x.dtype], self._stream()),

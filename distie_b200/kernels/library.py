@@ -61,6 +61,7 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_exp_gate_scan": ("state", [P, P, I, I, L, P, P, F, P, P, P, I, I, I, P, P, P, P]),
     "distie_stabilized_readout": ("state", [P, I, P, P, I, I, I, P]),
     "distie_route_top": ("routed", [P, I, P, I, I, I, I, P, P, I, P]),
+    "distie_route_pick": ("routed", [P, I, I, I, I, P, P, P]),
     "distie_routed_tile": ("routed", [I, I, I, I, I]),
     "distie_route_plan_words": ("routed", [I, I, I]),
     "distie_route_plan": ("routed", [P, P, I, I, I, I, P, P, P]),
