@@ -405,6 +405,14 @@ grouped_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, co
   }
 }
 
+// VEC consecutive elements as floats (16 bytes when VEC is 8 for bfloat16 or 4 for float; one element otherwise).
+template <typename T, int VEC>
+__device__ __forceinline__ void load_run(const T* p, float (&v)[VEC]) {
+  if constexpr (VEC == 8) load8(p, v);
+  else if constexpr (VEC == 4) { const float4 q = load4(p); v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
+  else v[0] = to_float(p[0]);
+}
+
 // ---- around the grouped product on the tcgen05 kernel (prompt portions in bfloat16) --------------------------------------
 // gathered[slot, :] = x[source[slot], :] (* scale[slot]): the rows sorted by expert, as the product's A operand.
 template <typename T>
@@ -415,6 +423,18 @@ __global__ void routed_gather_kernel(const T* __restrict__ x, int x_stride, int*
   const T* src = x + (size_t)plan.source[slot] * x_stride;
   const float scale = scale_in ? plan.scale[slot] : 1.f;
   T* dst = gathered + (size_t)slot * hidden;
+  constexpr int WIDE = sizeof(T) == 2 ? 8 : 4;
+  if (hidden % WIDE == 0 && x_stride % WIDE == 0 && (((uintptr_t)x | (uintptr_t)gathered) & 15) == 0) {
+    for (int c = threadIdx.x * WIDE; c < hidden; c += blockDim.x * WIDE) {  // 16 bytes a thread and round
+      float v[WIDE];
+      load_run<T, WIDE>(src + c, v);
+#pragma unroll
+      for (int i = 0; i < WIDE; ++i) v[i] *= scale;
+      if constexpr (WIDE == 8) store8(dst + c, v);
+      else store4(dst + c, make_float4(v[0], v[1], v[2], v[3]));
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = from_float<T>(to_float(src[c]) * scale);
 }
 
@@ -426,6 +446,13 @@ __global__ void routed_scatter_kernel(const float* __restrict__ y, int* __restri
   const float scale = scale_out ? plan.scale[slot] : 1.f;
   const float* src = y + (size_t)slot * hidden;
   float* dst = out + (size_t)plan.dest[slot] * hidden;
+  if (hidden % 4 == 0 && (((uintptr_t)y | (uintptr_t)out) & 15) == 0) {
+    for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(src + c);
+      *reinterpret_cast<float4*>(dst + c) = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = src[c] * scale;
 }
 
@@ -435,12 +462,6 @@ __global__ void routed_scatter_kernel(const float* __restrict__ y, int* __restri
 // round, all loads of a round independent of one another; no barrier inside the walk over K.
 constexpr int kRowsR = 8, kRowsWarps = 8;
 
-template <typename T, int VEC>
-__device__ __forceinline__ void load_run(const T* p, float (&v)[VEC]) {
-  if constexpr (VEC == 8) load8(p, v);
-  else if constexpr (VEC == 4) { const float4 q = load4(p); v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
-  else v[0] = to_float(p[0]);
-}
 
 template <typename T, bool SWIGLU, int VEC>
 __global__ void __launch_bounds__(kRowsWarps * 32)
