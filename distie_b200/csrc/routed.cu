@@ -464,7 +464,7 @@ constexpr int kRowsR = 8, kRowsWarps = 8;
 
 
 template <typename T, bool SWIGLU, int VEC>
-__global__ void __launch_bounds__(kRowsWarps * 32)
+__global__ void __launch_bounds__(kRowsWarps * 32, 3)
 grouped_rows_kernel(int rounds, const T* __restrict__ a, int a_stride, const T* __restrict__ w, int* __restrict__ plan_base, int pairs,
                     int experts, T* __restrict__ out, float* __restrict__ out32, int N, int K, int gather, int scale_in,
                     int scale_out) {

@@ -13,7 +13,7 @@ import torch
 
 from ..config.model_spec import PartSpec
 from ..kernels.interface import Terms
-from .base import FEED_FORWARDS, BuildContext, LayerRun, TensorSpec
+from .base import FEED_FORWARDS, Branches, BuildContext, LayerRun, TensorSpec
 from .linear import fuse_rows
 
 
@@ -72,8 +72,15 @@ class RoutedSwiGlu:
 
     def forward(self, x: torch.Tensor, run: LayerRun):
         k = self.kernels
-        ids, weights = k.route_top(x, self.router, self.top, "sigmoid")
-        out = Terms.of(k.routed_swiglu(x, ids, weights, self.gate_up, self.down, self.scale_input))
-        if self.shared_gate_up is not None:
-            out = out + Terms.of(k.linear_split(k.linear_swiglu(x, self.shared_gate_up), self.shared_down))
-        return out
+
+        def routed():
+            ids, weights = k.route_top(x, self.router, self.top, "sigmoid")
+            return k.routed_swiglu(x, ids, weights, self.gate_up, self.down, self.scale_input)
+
+        if self.shared_gate_up is None:
+            return Terms.of(routed())
+        # The routed experts and the shared one read the same input and nothing of one another: in a step of few
+        # tokens, where each is a chain of short kernels, they run side by side.
+        both = Branches.run([routed, lambda: k.linear_split(k.linear_swiglu(x, self.shared_gate_up), self.shared_down)],
+                            x.shape[0], x.device)
+        return Terms.of(both[0]) + Terms.of(both[1])
