@@ -737,6 +737,21 @@ gated_rmsnorm_vec_kernel(const float* __restrict__ x, int x_stride, Sliced gate,
 // ---------------------------------------------------------------------------
 // out[t, c] = act(x[t, c]) (* scale for c < scaled_columns), x a matrix or the slices of a split product.
 // ---------------------------------------------------------------------------
+// Four columns a thread: columns, scaled_columns and the strides multiples of 4, pointers 16-byte aligned.
+__global__ void activation_vec_kernel(Sliced x, float* __restrict__ out, int tokens, int columns, int silu, float scale,
+                                      int scaled_columns) {
+  const int quads = columns / 4;
+  const size_t total = (size_t)tokens * quads;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / quads;
+    const int c = (int)(idx % quads) * 4;
+    float4 v = x.at4(t, c);
+    if (silu) v = make_float4(silu_f(v.x), silu_f(v.y), silu_f(v.z), silu_f(v.w));
+    if (c < scaled_columns) v = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
+    *reinterpret_cast<float4*>(out + t * columns + c) = v;
+  }
+}
+
 __global__ void activation_kernel(Sliced x, float* __restrict__ out, int tokens, int columns, int silu, float scale,
                                   int scaled_columns) {
   const size_t total = (size_t)tokens * columns;
@@ -795,14 +810,50 @@ exp_gate_scan_kernel(float* __restrict__ state, const int* __restrict__ seq_boun
   for (int tile = first; tile < end; tile += tile_tokens) {
     const int count = min(tile_tokens, end - tile) * heads;
     const size_t base = (size_t)tile * heads;
-    for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
-      gates_s[idx] = keep[base + idx];
-      gates_s[plane + idx] = take[base + idx];
+    // (16 bytes a thread and round where the tile starts on a 16-byte boundary: all of a thread's loads in flight)
+    const bool quads = (base & 3) == 0 && (count & 3) == 0 && (plane & 3) == 0 &&
+                       (((uintptr_t)keep | (uintptr_t)take | (uintptr_t)floor_out) & 15) == 0;
+    if (quads) {
+#pragma unroll 4
+      for (int idx = threadIdx.x * 4; idx < count; idx += blockDim.x * 4) {
+        *reinterpret_cast<float4*>(gates_s + idx) = *reinterpret_cast<const float4*>(keep + base + idx);
+        *reinterpret_cast<float4*>(gates_s + plane + idx) = *reinterpret_cast<const float4*>(take + base + idx);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
+        gates_s[idx] = keep[base + idx];
+        gates_s[plane + idx] = take[base + idx];
+      }
     }
     __syncthreads();
     if (threadIdx.x < heads) {
-#pragma unroll 8
-      for (int at = threadIdx.x; at < count; at += heads) {
+      const int steps = count / heads;
+      int step = 0;
+      // Whole batches of eight tokens: sixteen loads, the chain in registers, twenty-four stores.
+      for (; step + 8 <= steps; step += 8) {
+        const int at0 = step * heads + threadIdx.x;
+        float f[8], i[8], a[8], b[8], c[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          f[u] = f_in[at0 + u * heads];
+          i[u] = i_in[at0 + u * heads];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float m_new = fmaxf(f[u] + m, i[u]);
+          a[u] = f[u] + m - m_new;
+          b[u] = i[u] - m_new;
+          c[u] = -m_new;
+          m = m_new;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          keep_o[at0 + u * heads] = a[u];
+          take_o[at0 + u * heads] = b[u];
+          floor_o[at0 + u * heads] = c[u];
+        }
+      }
+      for (int at = step * heads + threadIdx.x; at < count; at += heads) {
         const float f = f_in[at], i = i_in[at];
         const float m_new = fmaxf(f + m, i);
         keep_o[at] = f + m - m_new;
@@ -812,10 +863,19 @@ exp_gate_scan_kernel(float* __restrict__ state, const int* __restrict__ seq_boun
       }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
-      keep[base + idx] = keep_o[idx];
-      take[base + idx] = take_o[idx];
-      floor_out[base + idx] = floor_o[idx];
+    if (quads) {
+#pragma unroll 4
+      for (int idx = threadIdx.x * 4; idx < count; idx += blockDim.x * 4) {
+        *reinterpret_cast<float4*>(keep + base + idx) = *reinterpret_cast<const float4*>(keep_o + idx);
+        *reinterpret_cast<float4*>(take + base + idx) = *reinterpret_cast<const float4*>(take_o + idx);
+        *reinterpret_cast<float4*>(floor_out + base + idx) = *reinterpret_cast<const float4*>(floor_o + idx);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
+        keep[base + idx] = keep_o[idx];
+        take[base + idx] = take_o[idx];
+        floor_out[base + idx] = floor_o[idx];
+      }
     }
     __syncthreads();
   }
@@ -1081,6 +1141,15 @@ extern "C" int distie_activation(const float* x, int x_stride, int splits, long 
   if (tokens <= 0 || columns <= 0) return 0;
   if (splits < 1 || scaled_columns < 0 || scaled_columns > columns) return DISTIE_ERR_ARG;
   const size_t total = (size_t)tokens * columns;
+  if (columns % 4 == 0 && scaled_columns % 4 == 0 && x_stride % 4 == 0 && split_stride % 4 == 0 &&
+      (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+    const size_t quads = total / 4;
+    const unsigned vec_blocks = (unsigned)((quads + 255) / 256 > 148 * 16 ? 148 * 16 : (quads + 255) / 256);
+    activation_vec_kernel<<<vec_blocks, 256, 0, stream>>>(Sliced{x, x_stride, splits, split_stride}, out, tokens, columns,
+                                                         silu, scale, scaled_columns);
+    DISTIE_LAUNCH_CHECK();
+    return 0;
+  }
   const unsigned blocks = (unsigned)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
   activation_kernel<<<blocks, 256, 0, stream>>>(Sliced{x, x_stride, splits, split_stride}, out, tokens, columns, silu,
                                                scale, scaled_columns);
@@ -1104,8 +1173,15 @@ extern "C" int distie_exp_gate_scan(const float* log_in, const float* log_forget
                                               Sliced{log_forget, gate_stride, splits, split_stride}, in_bias, forget_bias,
                                               cap, tokens, heads, keep, take);
   DISTIE_LAUNCH_CHECK();
-  const int tile_tokens = heads <= 16 ? 128 : (2048 / heads < 1 ? 1 : 2048 / heads);
-  exp_gate_scan_kernel<<<num_seqs, 512, 5 * (size_t)tile_tokens * heads * sizeof(float), stream>>>(
+  // Tiles as long as 160 KB of shared memory allow (512 tokens up to 16 heads): a tile costs a round trip to memory
+  // on either side of its walk, which only a long tile makes small beside the walk.
+  int tile_tokens = 8192 / (heads < 16 ? 16 : heads);
+  if (tile_tokens < 1) tile_tokens = 1;
+  if (tile_tokens > tokens) tile_tokens = tokens;
+  const size_t scan_shared = 5 * (size_t)tile_tokens * heads * sizeof(float);
+  if (scan_shared > 48 * 1024)
+    cudaFuncSetAttribute(exp_gate_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)scan_shared);
+  exp_gate_scan_kernel<<<num_seqs, 512, scan_shared, stream>>>(
       state, seq_bounds, seq_seat, heads, tile_tokens, keep, take, floor_out);
   DISTIE_LAUNCH_CHECK();
   exp_three_kernel<<<blocks, 256, 0, stream>>>(keep, take, floor_out, total);
