@@ -146,11 +146,20 @@ qk_rope_norm_write_kernel(SlicedRows qk, const float* __restrict__ bias, T* __re
                           T* __restrict__ v_cache, int num_heads, int num_kv_heads, int head_dim, int rotary_dim,
                           int interleaved, int page_size, int num_pages, int write, int normed, float norm_eps,
                           int* __restrict__ error) {
-  extern __shared__ __align__(16) float heads_s[];  // kRopeWarps pieces of head_dim floats
+  extern __shared__ __align__(16) float heads_s[];  // kRopeWarps pieces of head_dim floats, then cos and sin of the token
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* head_s = heads_s + (size_t)warp * head_dim;
   const int pos = positions[t];
   const int half = rotary_dim / 2;
+  float* cos_s = heads_s + (size_t)kRopeWarps * head_dim;  // the token's angles serve all of its heads
+  float* sin_s = cos_s + half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn, cs;
+    sincosf((float)pos * inv_freq[i], &sn, &cs);
+    cos_s[i] = cs * factor;
+    sin_s[i] = sn * factor;
+  }
+  __syncthreads();
   int page = -1;
   if (write) {
     const int seat = seq_seat[token_seq[t]];
@@ -175,10 +184,7 @@ qk_rope_norm_write_kernel(SlicedRows qk, const float* __restrict__ bias, T* __re
     float ss = 0.f;
     for (int i = lane; i < half; i += 32) {  // every pair is read and written by one lane
       const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
-      float sn, cs;
-      sincosf((float)pos * inv_freq[i], &sn, &cs);
-      sn *= factor;
-      cs *= factor;
+      const float sn = sin_s[i], cs = cos_s[i];
       const float u = head_s[a], v = head_s[b];
       const float ru = u * cs - v * sn, rv = v * cs + u * sn;
       head_s[a] = ru;
@@ -270,7 +276,7 @@ extern "C" int distie_qk_rope_norm_write(const float* qk, int qk_stride, int spl
   // Few tokens: the heads of a token spread over several blocks, so that the step fills more of the machine.
   const dim3 grid(tokens, tokens < 512 ? (num_heads + num_kv_heads + kRopeWarps - 1) / kRopeWarps : 1);
   const int threads = kRopeWarps * 32;
-  const size_t shared = (size_t)kRopeWarps * head_dim * sizeof(float);
+  const size_t shared = ((size_t)kRopeWarps * head_dim + rotary_dim) * sizeof(float);
   const SlicedRows rows{qk, qk_stride, splits, split_stride};
   if (dtype == DISTIE_BF16)
     qk_rope_norm_write_kernel<<<grid, threads, shared, stream>>>(
